@@ -1,10 +1,11 @@
 from .base import (ConfigError, ModelConfig, architecture_name, config_from_dict, load_config,
                    register_architecture, resolve_architecture, supported_architectures)
 from .kedanex import KedanexConfig
+from .mifolorn import MifolornConfig
 from .padodra import PadodraConfig
 from .qwen3 import Qwen3Config
 
 __all__ = [
-    "ConfigError", "KedanexConfig", "ModelConfig", "PadodraConfig", "Qwen3Config", "architecture_name", "config_from_dict", "load_config",
+    "ConfigError", "KedanexConfig", "MifolornConfig", "ModelConfig", "PadodraConfig", "Qwen3Config", "architecture_name", "config_from_dict", "load_config",
     "register_architecture", "resolve_architecture", "supported_architectures",
 ]

@@ -890,3 +890,88 @@ HK_API int hk_latent_prep(const float* proj, long long ld, void* q_plain, void* 
                          page_tokens, write_kv);
   return HK_ERR_UNSUPPORTED;
 }
+
+// ----------------------------------------------------------------------------- sums of float32 streams
+// out = (accumulate ? out : 0) + alpha * a + beta * b, element by element (b may be null): the sum of two mixers that
+// read the same input, each with a factor of its own; a stream that is added to the residual again.
+__global__ void scaled_sum_kernel(float* __restrict__ out, const float* __restrict__ a, float alpha, const float* __restrict__ b,
+                                  float beta, long long total4, long long total, int accumulate) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total4) {
+    const float4 x = reinterpret_cast<const float4*>(a)[i];
+    float4 r = accumulate ? reinterpret_cast<float4*>(out)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    r.x = fmaf(alpha, x.x, r.x); r.y = fmaf(alpha, x.y, r.y); r.z = fmaf(alpha, x.z, r.z); r.w = fmaf(alpha, x.w, r.w);
+    if (b != nullptr) {
+      const float4 y = reinterpret_cast<const float4*>(b)[i];
+      r.x = fmaf(beta, y.x, r.x); r.y = fmaf(beta, y.y, r.y); r.z = fmaf(beta, y.z, r.z); r.w = fmaf(beta, y.w, r.w);
+    }
+    reinterpret_cast<float4*>(out)[i] = r;
+  }
+  if (i < total - 4 * total4) {                  // the last one to three elements
+    const long long j = 4 * total4 + i;
+    float r = accumulate ? out[j] : 0.f;
+    r = fmaf(alpha, a[j], r);
+    if (b != nullptr) r = fmaf(beta, b[j], r);
+    out[j] = r;
+  }
+}
+
+HK_API int hk_scaled_sum(float* out, const float* a, float alpha, const float* b, float beta, long long total, int accumulate,
+                         void* stream) {
+  if (total <= 0) return 0;
+  const bool vec = !(((uintptr_t)out | (uintptr_t)a | (uintptr_t)b) & 15);
+  const long long total4 = vec ? total / 4 : 0;
+  const long long threads = total4 > total - 4 * total4 ? total4 : total - 4 * total4;
+  return hk_launch(scaled_sum_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, out, a, alpha, b,
+                   beta, total4, total, accumulate);
+}
+
+// ----------------------------------------------------------------------------- a float32 stream rounded to the storage type
+template <typename T>
+__global__ void narrow_kernel(const float* __restrict__ x, T* __restrict__ out, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) out[i] = from_f32<T>(x[i]);
+}
+
+HK_API int hk_narrow(const float* x, void* out, int out_dtype, long long total, void* stream) {
+  if (total <= 0) return 0;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (out_dtype == HK_BF16) return hk_launch(narrow_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, x, (bf16*)out, total);
+  if (out_dtype == HK_F32) return hk_launch(narrow_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, x, (float*)out, total);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ----------------------------------------------------------------------------- a gate times a token's own vector
+// out[t, j] = act(z[t, j]) * table[ids[t], col0 + j] for j < W: z is a float32 column slice (row stride ld) of a
+// projection's output, the table [vocab, table_cols] holds one vector per token id of which a layer reads W columns
+// from col0 on.  act 0: gelu in its tanh form, 1: silu.
+template <typename TT, typename TO>
+__global__ void token_gate_kernel(const float* __restrict__ z, long long ld, const TT* __restrict__ table, long long table_cols,
+                                  int col0, const int* __restrict__ ids, TO* __restrict__ out, long long total, int W, int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / W;
+  const int j = (int)(i % W);
+  const float g = z[t * ld + j];
+  const float a = act == 0 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) : g / (1.0f + expf(-g));
+  out[i] = from_f32<TO>(a * to_f32<TT>(table[(size_t)ids[t] * table_cols + col0 + j]));
+}
+
+HK_API int hk_token_gate(const float* z, long long ld, const void* table, int table_dtype, long long table_cols, int col0,
+                         const int* ids, void* out, int out_dtype, int n, int W, int act, void* stream) {
+  if (n <= 0 || W <= 0) return 0;
+  if (act < 0 || act > 1 || col0 < 0 || col0 + W > table_cols) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)n * W;
+  const dim3 grid((unsigned)((total + 255) / 256)), block(256);
+  if (table_dtype == HK_F32 && out_dtype == HK_F32)
+    return hk_launch(token_gate_kernel<float, float>, grid, block, 0, s, z, ld, (const float*)table, table_cols, col0, ids, (float*)out,
+                     total, W, act);
+  if (table_dtype == HK_BF16 && out_dtype == HK_BF16)
+    return hk_launch(token_gate_kernel<bf16, bf16>, grid, block, 0, s, z, ld, (const bf16*)table, table_cols, col0, ids, (bf16*)out, total,
+                     W, act);
+  if (table_dtype == HK_F32 && out_dtype == HK_BF16)
+    return hk_launch(token_gate_kernel<float, bf16>, grid, block, 0, s, z, ld, (const float*)table, table_cols, col0, ids, (bf16*)out,
+                     total, W, act);
+  return HK_ERR_UNSUPPORTED;
+}

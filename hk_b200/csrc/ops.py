@@ -637,6 +637,161 @@ def mingru_scan(proj, z_bias, x_bias, segments, state, out) -> None:
                               int(segments.shape[0]), _ptr(state), _ptr(out), _dt(out), W, _stream()), "mingru_scan")
 
 
+def short_conv(x, weight, segments, tail, out) -> None:
+    """out[t, c] = silu(sum_j weight[c, j] * x[t - (taps - 1) + j, c]) over the rows of every segment (the last column
+    of `weight` is the current token's).  Rows before a segment's first come from `tail` float32 [slots, taps - 1, C],
+    the request's last taps - 1 inputs (zero at its start), which is moved on.  x and out: float32 column slices [n, C]."""
+    C = int(weight.shape[0])
+    ldx, ldy = _cols(x, "x", C), _cols(out, "out", C)
+    _need(weight, "weight", torch.float32, 2)
+    _need(segments, "segments", torch.int32, 2)
+    _need(tail, "tail", torch.float32, 3)
+    taps = int(weight.shape[1])
+    if x.shape[0] != out.shape[0] or tuple(tail.shape[1:]) != (taps - 1, C) or segments.shape[1] != 3 or taps < 2:
+        raise KernelError("short_conv: shapes do not fit")
+    lib = build.load("recurrent")
+    _check(lib.hk_short_conv(_ptr(x), ctypes.c_longlong(ldx), _ptr(weight), _ptr(segments), int(segments.shape[0]), int(x.shape[0]),
+                             _ptr(tail), _ptr(out), ctypes.c_longlong(ldy), C, taps, _stream()), "short_conv")
+
+
+def gated_delta_scan(q, k, v, b_logit, a_logit, a_log, dt_bias, segments, state, out, n_heads: int, n_qk_heads: int,
+                     key_dim: int, value_dim: int, q_scale: float, unit_eps: float) -> None:
+    """Gated delta rule over the rows of every segment, per head, S = state[slot, head] float32 [dk, dv]:
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  out = S^T q
+    with q, k made unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale, beta = sigmoid(b_logit),
+    g = exp(-exp(a_log) * softplus(a_logit + dt_bias)).  q, k [n, G*dk] and v [n, H*dv]: float32 column slices of ONE
+    matrix; b_logit, a_logit [n, H] slices of one; value head h reads query/key head h // (H/G).  out float32 [n, H*dv]."""
+    H, G, dk, dv = n_heads, n_qk_heads, key_dim, value_dim
+    ld = _cols(q, "q", G * dk)
+    if _cols(k, "k", G * dk) != ld or _cols(v, "v", H * dv) != ld:
+        raise KernelError("gated_delta_scan: q, k and v must be slices of one matrix")
+    ldg = _cols(b_logit, "b_logit", H)
+    if _cols(a_logit, "a_logit", H) != ldg:
+        raise KernelError("gated_delta_scan: b_logit and a_logit must be slices of one matrix")
+    _need(a_log, "a_log", torch.float32, 1)
+    _need(dt_bias, "dt_bias", torch.float32, 1)
+    _need(segments, "segments", torch.int32, 2)
+    _need(state, "state", torch.float32, 4)
+    _need(out, "out", torch.float32, 2)
+    n = q.shape[0]
+    if tuple(state.shape[1:]) != (H, dk, dv) or tuple(out.shape) != (n, H * dv) or segments.shape[1] != 3 \
+            or a_log.shape[0] != H or dt_bias.shape[0] != H or H % G:
+        raise KernelError("gated_delta_scan: shapes do not fit")
+    lib = build.load("recurrent")
+    rec = torch.empty(n * H * int(lib.hk_delta_rule_record(dk, dv)), dtype=torch.float32, device=out.device)
+    _check(lib.hk_gated_delta_scan(_ptr(q), _ptr(k), _ptr(v), ctypes.c_longlong(ld), _ptr(b_logit), _ptr(a_logit),
+                                   ctypes.c_longlong(ldg), _ptr(a_log), _ptr(dt_bias), _ptr(segments), int(segments.shape[0]), n,
+                                   _ptr(rec), _ptr(state), _ptr(out), H, G, dk, dv, ctypes.c_float(q_scale),
+                                   ctypes.c_float(unit_eps), _stream()), "gated_delta_scan", launches=2)
+
+
+def mlstm_padded(value_dim: int) -> int:
+    """The value size of the mLSTM's state and scan output: value_dim + 1 (the normaliser's column) rounded up to 4."""
+    return (int(value_dim) + 1 + 3) & ~3
+
+
+def mlstm_scan(q, k, v, i_logit, f_logit, i_bias, f_bias, segments, state, m_state, out, gates, n_heads: int, key_dim: int,
+               value_dim: int, cap: float, q_scale: float) -> None:
+    """Matrix memory with exponential gates over the rows of every segment, per head (S, n zero and m = 0 at a
+    request's start): i = cap tanh((i_logit + i_bias) / cap), f = logsigmoid(cap tanh((f_logit + f_bias) / cap)),
+        m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise with k alone.
+    state float32 [slots, H, dk, dvp] holds S and, as column dv, n (dvp = mlstm_padded(dv)); m_state [slots, H].
+    out float32 [n, H*dvp]: per head S^T (q q_scale) and, at column dv, n . (q q_scale); gates float32 [n, H, 3]
+    receives (e^(f + m - m'), e^(i - m'), e^(-m')) per token.  q, k, v, i_logit, f_logit: slices of ONE float32 matrix."""
+    H, dk, dv = n_heads, key_dim, value_dim
+    dvp = mlstm_padded(dv)
+    ld = _cols(q, "q", H * dk)
+    if _cols(k, "k", H * dk) != ld or _cols(v, "v", H * dv) != ld or _cols(i_logit, "i_logit", H) != ld \
+            or _cols(f_logit, "f_logit", H) != ld:
+        raise KernelError("mlstm_scan: q, k, v and the gates' logits must be slices of one matrix")
+    _need(i_bias, "i_bias", torch.float32, 1)
+    _need(f_bias, "f_bias", torch.float32, 1)
+    _need(segments, "segments", torch.int32, 2)
+    _need(state, "state", torch.float32, 4)
+    _need(m_state, "m_state", torch.float32, 2)
+    _need(out, "out", torch.float32, 2)
+    _need(gates, "gates", torch.float32, 3)
+    n = q.shape[0]
+    if tuple(state.shape[1:]) != (H, dk, dvp) or tuple(m_state.shape[1:]) != (H,) or tuple(out.shape) != (n, H * dvp) \
+            or tuple(gates.shape) != (n, H, 3) or segments.shape[1] != 3 or i_bias.shape[0] != H or f_bias.shape[0] != H:
+        raise KernelError("mlstm_scan: shapes do not fit")
+    lib = build.load("recurrent")
+    rec = torch.empty(n * H * int(lib.hk_delta_rule_record(dk, dvp)), dtype=torch.float32, device=out.device)
+    _check(lib.hk_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(i_logit), _ptr(f_logit), ctypes.c_longlong(ld), _ptr(i_bias),
+                             _ptr(f_bias), _ptr(segments), int(segments.shape[0]), n, _ptr(rec), _ptr(gates), _ptr(state),
+                             _ptr(m_state), _ptr(out), H, dk, dv, ctypes.c_float(cap), ctypes.c_float(q_scale), _stream()),
+           "mlstm_scan", launches=3)
+
+
+def head_out_gate(o, gate_logit, weight, eps: float, out, n_heads: int, value_dim: int, act: str = "sigmoid",
+                  gates=None, den_eps: float = 0.0) -> None:
+    """out[t, h, :] = N(o[t, h, :dv] / den) * weight * act(gate_logit[t, h, :]), N = x / sqrt(mean(x^2) + eps) over the
+    head's dv values.  o float32 [n, H*ldo] with ldo >= dv floats per head; weight [H*dv], or [dv] shared by the heads;
+    act 'sigmoid' or 'silu'.  With `gates` (float32 [n, H, 3], as `mlstm_scan` leaves it) den = max(|o[t, h, dv]|,
+    gates[t, h, 2]) + den_eps; without, den = 1."""
+    H, dv = n_heads, value_dim
+    _need(o, "o", torch.float32, 2)
+    ldg = _cols(gate_logit, "gate_logit", H * dv)
+    _need(weight, "weight", torch.float32, 1)
+    _need(out, "out", dims=2)
+    n = out.shape[0]
+    if o.shape[0] != n or o.shape[1] % H or tuple(out.shape) != (n, H * dv) or weight.shape[0] not in (dv, H * dv) \
+            or gate_logit.shape[0] != n or act not in ("sigmoid", "silu"):
+        raise KernelError("head_out_gate: shapes do not fit")
+    ldo = o.shape[1] // H
+    if gates is not None:
+        _need(gates, "gates", torch.float32, 3)
+        if tuple(gates.shape) != (n, H, 3):
+            raise KernelError("head_out_gate: gates must be [n, H, 3]")
+    shared = 1 if (weight.shape[0] == dv and H > 1) else 0
+    lib = build.load("recurrent")
+    _check(lib.hk_head_out_gate(_ptr(o), int(ldo), _ptr(gate_logit), ctypes.c_longlong(ldg), _ptr(weight), shared,
+                                0 if act == "sigmoid" else 1, _ptr(gates), ctypes.c_float(den_eps), _ptr(out), _dt(out), n, H, dv,
+                                ctypes.c_float(eps), _stream()), "head_out_gate")
+
+
+# ---- small element-wise kernels of layers with several streams -------------------------------
+
+
+def scaled_sum(out, a, alpha: float, b=None, beta: float = 0.0, accumulate: bool = True) -> None:
+    """out (+)= alpha * a + beta * b, all float32 of one shape (b may be absent); stored instead of added without
+    `accumulate`."""
+    _need(out, "out", torch.float32)
+    _need(a, "a", torch.float32)
+    if b is not None:
+        _need(b, "b", torch.float32)
+    if a.shape != out.shape or (b is not None and b.shape != out.shape):
+        raise KernelError("scaled_sum: shapes differ")
+    lib = build.load("elementwise")
+    _check(lib.hk_scaled_sum(_ptr(out), _ptr(a), ctypes.c_float(alpha), _ptr(b), ctypes.c_float(beta),
+                             ctypes.c_longlong(out.numel()), 1 if accumulate else 0, _stream()), "scaled_sum")
+
+
+def narrow(x, out) -> None:
+    """out = x (float32) rounded to out's type, element by element."""
+    _need(x, "x", torch.float32)
+    _need(out, "out")
+    if x.shape != out.shape:
+        raise KernelError("narrow: shapes differ")
+    lib = build.load("elementwise")
+    _check(lib.hk_narrow(_ptr(x), _ptr(out), _dt(out), ctypes.c_longlong(x.numel()), _stream()), "narrow")
+
+
+def token_gate(z, table, col0: int, token_ids, out, act: str = "gelu_tanh") -> None:
+    """out[t, j] = act(z[t, j]) * table[token_ids[t], col0 + j] for the W = out.shape[1] columns from col0 on; z a
+    float32 column slice [n, W]; act 'gelu_tanh' or 'silu'."""
+    _need(out, "out", dims=2)
+    n, W = out.shape
+    ld = _cols(z, "z", W)
+    _need(table, "table", dims=2)
+    _need(token_ids, "token_ids", torch.int32, 1)
+    if z.shape[0] != n or token_ids.shape[0] != n or act not in ("gelu_tanh", "silu"):
+        raise KernelError("token_gate: shapes do not fit")
+    lib = build.load("elementwise")
+    _check(lib.hk_token_gate(_ptr(z), ctypes.c_longlong(ld), _ptr(table), _dt(table), ctypes.c_longlong(table.shape[1]), int(col0),
+                             _ptr(token_ids), _ptr(out), _dt(out), n, W, 0 if act == "gelu_tanh" else 1, _stream()), "token_gate")
+
+
 # ---- routed feed-forward -------------------------------------------------------------------
 
 

@@ -290,28 +290,20 @@ static int dr_launch(int L, dim3 grid, int threads, size_t smem, cudaStream_t s,
 #undef DR_LAUNCH
 }
 
-// `rec`: scratch of n_rows * H * hk_delta_rule_record(dk, dv) floats (16-byte aligned) that the call fills and reads.
-HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, const float* al, long long ld, const float* wl,
-                              long long ldw, const float* a_bias, const float* w_bias, const int* segs, int n_seg, int n_rows,
-                              float* rec, float* state, float* out, int H, int dk, int dv, float decay_scale, float key_eps,
-                              void* stream) {
-  if (n_seg <= 0 || n_rows <= 0) return 0;
-  if (H < 1 || dk < 1 || dv < 1 || dk > 2048 || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
-  cudaStream_t s = (cudaStream_t)stream;
-  // lanes per column: one where requests x heads x columns alone give every SM four warps or more, else as many as that takes
+// Lanes per column for a step: one where requests x heads x columns alone give every SM four warps or more, else as many
+// as that takes.  Returns 0 for a key size that no layout holds.
+static int dr_plan(int n_seg, int H, int dk, int dv, int* L_out, int* rpt_out) {
   const long long warps1 = ((long long)n_seg * H * dv + 31) / 32;
   int spread = 1;
   while (spread < 32 && warps1 * spread < 4 * 148) spread <<= 1;
-  int L, rpt;
-  dr_layout(dk, spread, &L, &rpt);
-  if (!rpt) return HK_ERR_UNSUPPORTED;
+  dr_layout(dk, spread, L_out, rpt_out);
+  return *rpt_out;
+}
+
+// The scan over records that a prep kernel wrote with the layout (L, rpt) of `dr_plan`.
+static int dr_scan_records(const float* rec, const int* segs, int n_seg, float* state, float* out, int H, int dk, int dv, int L,
+                           int rpt, cudaStream_t s) {
   const int R = 5 * L * rpt + dv;
-  {
-    const long long items = (long long)n_rows * H;
-    int e = hk_launch(delta_rule_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, r, k, v, al, ld, wl, ldw, a_bias,
-                      w_bias, rec, items, H, dk, dv, L, rpt, decay_scale, key_eps);
-    if (e) return e;
-  }
   if (dv & 3) {
     const int cols = max(1, min(dv, 128 / L));
     const int threads = ((cols * L + 31) / 32) * 32;      // whole warps: the lanes of a column meet by shuffle
@@ -320,7 +312,7 @@ HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, co
     int e = hk_allow_smem(delta_rule_scan_plain_kernel, smem, cache);
     if (e) return e;
     return hk_launch(delta_rule_scan_plain_kernel, dim3((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols)), dim3(threads), smem, s,
-                     (const float*)rec, segs, state, out, H, dk, dv, L, rpt, cols);
+                     rec, segs, state, out, H, dk, dv, L, rpt, cols);
   }
   // a block takes as many columns as 256 threads hold (they share the records that the ring brings), fewer while the
   // blocks do not yet fill the SMs twice: one request of 2,048 tokens at 32 heads of 64 runs 808 us with 8 columns a
@@ -343,6 +335,25 @@ HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, co
   if (rpt == 16) return dr_launch<16, 1>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
   if (rpt == 32) return dr_launch<32, 1>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
   return dr_launch<64, 1>(L, grid, threads, smem, s, rec, segs, state, out, H, dk, dv, cols, chunk);
+}
+
+// `rec`: scratch of n_rows * H * hk_delta_rule_record(dk, dv) floats (16-byte aligned) that the call fills and reads.
+HK_API int hk_delta_rule_scan(const float* r, const float* k, const float* v, const float* al, long long ld, const float* wl,
+                              long long ldw, const float* a_bias, const float* w_bias, const int* segs, int n_seg, int n_rows,
+                              float* rec, float* state, float* out, int H, int dk, int dv, float decay_scale, float key_eps,
+                              void* stream) {
+  if (n_seg <= 0 || n_rows <= 0) return 0;
+  if (H < 1 || dk < 1 || dv < 1 || dk > 2048 || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  int L, rpt;
+  if (!dr_plan(n_seg, H, dk, dv, &L, &rpt)) return HK_ERR_UNSUPPORTED;
+  {
+    const long long items = (long long)n_rows * H;
+    int e = hk_launch(delta_rule_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, r, k, v, al, ld, wl, ldw, a_bias,
+                      w_bias, rec, items, H, dk, dv, L, rpt, decay_scale, key_eps);
+    if (e) return e;
+  }
+  return dr_scan_records(rec, segs, n_seg, state, out, H, dk, dv, L, rpt, s);
 }
 
 // ------------------------------------------------------------------ generalised delta rule: the output's gate
@@ -470,5 +481,263 @@ HK_API int hk_mingru_scan(const float* proj, long long ld, const float* z_bias, 
     return hk_launch(mingru_scan_kernel<float>, grid, dim3(32 * MG_LANES), 0, s, proj, ld, z_bias, x_bias, segs, state, (float*)out, W);
   if (out_dtype == HK_BF16)
     return hk_launch(mingru_scan_kernel<bf16>, grid, dim3(32 * MG_LANES), 0, s, proj, ld, z_bias, x_bias, segs, state, (bf16*)out, W);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ------------------------------------------------------------------ short causal convolution per channel
+// y[t, c] = act(sum_j w[c, j] * x[t - (taps - 1) + j, c]) over the rows of every segment, with act = silu: the last
+// column of w is the current token's.  The inputs before a segment's first row come from the request's tail
+// (state [slots, taps - 1, C], the last taps - 1 inputs of the request, zero at its start), which the same call
+// moves on.  x and y are column slices [n, C] of wider float32 matrices.  A thread owns one channel of one chunk
+// of a segment's tokens; the threads of the first chunk read the old tail before they write the new one, and
+// nobody else touches it.
+#define SC_TOKENS 32
+#define SC_MAX_TAPS 16
+
+__global__ void __launch_bounds__(128)
+short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w, const int* __restrict__ segs,
+                  float* __restrict__ tail, float* __restrict__ y, long long ldy, int C, int taps) {
+  const int seg = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
+  const int t0 = blockIdx.z * SC_TOKENS;
+  if (c >= C || t0 >= count) return;
+  const int back = taps - 1;
+  float* tl = tail + (size_t)slot * back * C + c;
+  float wc[SC_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < SC_MAX_TAPS; ++j) wc[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+  auto input = [&](int r) -> float {            // the request's input r rows from the segment's first (r may be negative)
+    return r >= 0 ? x[(size_t)(row0 + r) * ldx + c] : tl[(size_t)(back + r) * C];
+  };
+  const int t1 = min(count, t0 + SC_TOKENS);
+  for (int t = t0; t < t1; ++t) {
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < SC_MAX_TAPS; ++j)
+      if (j < taps) acc = fmaf(wc[j], input(t - back + j), acc);
+    y[(size_t)(row0 + t) * ldy + c] = acc / (1.0f + expf(-acc));
+  }
+  if (blockIdx.z == 0 && back > 0) {
+    float keep[SC_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < SC_MAX_TAPS; ++j)
+      if (j < back) keep[j] = input(count - back + j);
+#pragma unroll
+    for (int j = 0; j < SC_MAX_TAPS; ++j)
+      if (j < back) tl[(size_t)j * C] = keep[j];
+  }
+}
+
+HK_API int hk_short_conv(const float* x, long long ldx, const float* w, const int* segs, int n_seg, int n_rows, float* tail,
+                         float* y, long long ldy, int C, int taps, void* stream) {
+  if (n_seg <= 0 || n_rows <= 0 || C <= 0) return 0;
+  if (taps < 1 || taps > SC_MAX_TAPS) return HK_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)n_seg, (unsigned)((C + 127) / 128), (unsigned)((n_rows + SC_TOKENS - 1) / SC_TOKENS));
+  return hk_launch(short_conv_kernel, grid, dim3(128), 0, (cudaStream_t)stream, x, ldx, w, segs, tail, y, ldy, C, taps);
+}
+
+// ------------------------------------------------------------------ gated delta rule
+// Per head a matrix state S [dk, dv] and per token a scalar decay g and a scalar write strength beta:
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// with q and k unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times q_scale, g = exp(-exp(A_log) *
+// softplus(a_logit + dt_bias)), beta = sigmoid(b_logit).  Query/key head h / (H / G) serves value head h.  Written out,
+// S_new = g S - (g beta k)(k^T S) + k (beta v)^T, which is the generalised rule's record (d, a*u, u, k, r, v) =
+// (g, g beta k, k, k, q, beta v): the scan above runs it.
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+__global__ void gated_delta_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                        long long ld, const float* __restrict__ bl, const float* __restrict__ al, long long ldg,
+                                        const float* __restrict__ a_log, const float* __restrict__ dt_bias, float* __restrict__ rec,
+                                        long long items, int H, int G, int dk, int dv, int L, int RPT, float q_scale,
+                                        float unit_eps) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const size_t row = (size_t)(item / H);
+  const int h = (int)(item % H);
+  const int g = h / (H / G);
+  const float* qp = q + row * ld + (size_t)g * dk;
+  const float* kp = k + row * ld + (size_t)g * dk;
+  float sq = 0.f, sk = 0.f;
+  for (int i = lane; i < dk; i += 32) {
+    const float a = qp[i], b = kp[i];
+    sq = fmaf(a, a, sq);
+    sk = fmaf(b, b, sk);
+  }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  const float qinv = q_scale / sqrtf(sq + unit_eps), kinv = 1.0f / sqrtf(sk + unit_eps);
+  const float beta = sigmoid_f(bl[row * ldg + h]);
+  const float decay = expf(-expf(a_log[h]) * softplus_f(al[row * ldg + h] + dt_bias[h]));
+  const int P = L * RPT;
+  float* out = rec + (size_t)item * (5 * P + dv);
+  for (int j = lane; j < P; j += 32) {
+    const int i = (j % RPT) * L + j / RPT;       // the entry that sits at place j
+    float d = 0.f, au = 0.f, u = 0.f, rv = 0.f;
+    if (i < dk) {
+      u = kp[i] * kinv;
+      au = decay * beta * u;
+      d = decay;
+      rv = qp[i] * qinv;
+    }
+    out[j] = d;
+    out[P + j] = au;
+    out[2 * P + j] = u;
+    out[3 * P + j] = u;
+    out[4 * P + j] = rv;
+  }
+  for (int c = lane; c < dv; c += 32) out[5 * P + c] = beta * v[row * ld + (size_t)h * dv + c];
+}
+
+// q, k [n, G*dk] and v [n, H*dv] are column slices of one float32 matrix (row stride ld), already convolved and
+// activated; b_logit and a_logit [n, H] slices of one (row stride ldg).  `rec` as for hk_delta_rule_scan.
+HK_API int hk_gated_delta_scan(const float* q, const float* k, const float* v, long long ld, const float* bl, const float* al,
+                               long long ldg, const float* a_log, const float* dt_bias, const int* segs, int n_seg, int n_rows,
+                               float* rec, float* state, float* out, int H, int G, int dk, int dv, float q_scale, float unit_eps,
+                               void* stream) {
+  if (n_seg <= 0 || n_rows <= 0) return 0;
+  if (H < 1 || G < 1 || H % G || dk < 1 || dv < 1 || dk > 2048 || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  int L, rpt;
+  if (!dr_plan(n_seg, H, dk, dv, &L, &rpt)) return HK_ERR_UNSUPPORTED;
+  const long long items = (long long)n_rows * H;
+  int e = hk_launch(gated_delta_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, q, k, v, ld, bl, al, ldg, a_log,
+                    dt_bias, rec, items, H, G, dk, dv, L, rpt, q_scale, unit_eps);
+  if (e) return e;
+  return dr_scan_records(rec, segs, n_seg, state, out, H, dk, dv, L, rpt, s);
+}
+
+// ------------------------------------------------------------------ matrix memory with exponential gates (mLSTM)
+// Per head a matrix S [dk, dv], a vector n [dk] and a running maximum m (0 at a request's start).  With the log input
+// gate i = cap tanh((il + bi) / cap) and the log forget gate f = logsigmoid(cap tanh((fl + bf) / cap)):
+//     m_t = max(f + m_(t-1), i);  S_t = e^(f + m_(t-1) - m_t) S_(t-1) + e^(i - m_t) k v^T;  n_t likewise with k alone
+//     o = S_t^T q / (max(|n_t . q|, e^(-m_t)) + den_eps)
+// The maxima are a scalar recurrence per (request, head): one thread walks it and leaves, per token, the three
+// exponentials.  n rides along as one more column of S whose value is always 1 (the state is [dk, dvp] with
+// dvp = dv + 1 rounded up to 4; the columns past dv + 1 stay zero), so the delta rule's scan runs the matrix part
+// with the record (d, a*u, u, k, r, v) = (keep, 0, 0, take k, q, [v | 1 | 0..]) and hands back S^T q and n . q together.
+__device__ __forceinline__ float logsigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+__global__ void mlstm_gates_kernel(const float* __restrict__ il, const float* __restrict__ fl, long long ld,
+                                   const float* __restrict__ i_bias, const float* __restrict__ f_bias, const int* __restrict__ segs,
+                                   float* __restrict__ m_state, float* __restrict__ gates, int n_seg, int H, float cap) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_seg * H) return;
+  const int seg = idx / H, h = idx % H;
+  const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
+  const float bi = i_bias[h], bf = f_bias[h];
+  float m = m_state[(size_t)slot * H + h];
+  for (int t = 0; t < count; ++t) {
+    const size_t row = (size_t)(row0 + t);
+    const float ig = cap * tanhf((il[row * ld + h] + bi) / cap);
+    const float fg = logsigmoid_f(cap * tanhf((fl[row * ld + h] + bf) / cap));
+    const float mn = fmaxf(fg + m, ig);
+    float* o = gates + (row * H + h) * 3;
+    o[0] = expf(fg + m - mn);
+    o[1] = expf(ig - mn);
+    o[2] = expf(-mn);
+    m = mn;
+  }
+  m_state[(size_t)slot * H + h] = m;
+}
+
+__global__ void mlstm_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                  long long ld, const float* __restrict__ gates, float* __restrict__ rec, long long items, int H,
+                                  int dk, int dv, int dvp, int L, int RPT, float q_scale) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const size_t row = (size_t)(item / H);
+  const int h = (int)(item % H);
+  const float keep = gates[item * 3], take = gates[item * 3 + 1];
+  const float* qp = q + row * ld + (size_t)h * dk;
+  const float* kp = k + row * ld + (size_t)h * dk;
+  const int P = L * RPT;
+  float* out = rec + (size_t)item * (5 * P + dvp);
+  for (int j = lane; j < P; j += 32) {
+    const int i = (j % RPT) * L + j / RPT;
+    const bool in = i < dk;
+    out[j] = in ? keep : 0.f;
+    out[P + j] = 0.f;
+    out[2 * P + j] = 0.f;
+    out[3 * P + j] = in ? take * kp[i] : 0.f;
+    out[4 * P + j] = in ? qp[i] * q_scale : 0.f;
+  }
+  for (int c = lane; c < dvp; c += 32) out[5 * P + c] = c < dv ? v[row * ld + (size_t)h * dv + c] : (c == dv ? 1.0f : 0.f);
+}
+
+// The padded value size of the mLSTM's state and scan output.
+HK_API int hk_mlstm_padded(int dv) { return (dv + 1 + 3) & ~3; }
+
+// q, k [n, H*dk], v [n, H*dv], il, fl [n, H]: column slices of one float32 matrix (row stride ld).  state
+// [slots, H, dk, dvp], m_state [slots, H], gates scratch [n, H, 3] (kept: the output's gate reads e^(-m)), out [n, H*dvp].
+HK_API int hk_mlstm_scan(const float* q, const float* k, const float* v, const float* il, const float* fl, long long ld,
+                         const float* i_bias, const float* f_bias, const int* segs, int n_seg, int n_rows, float* rec,
+                         float* gates, float* state, float* m_state, float* out, int H, int dk, int dv, float cap, float q_scale,
+                         void* stream) {
+  if (n_seg <= 0 || n_rows <= 0) return 0;
+  if (H < 1 || dk < 1 || dv < 1 || dk > 2048 || !(cap > 0.f) || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int dvp = hk_mlstm_padded(dv);
+  int L, rpt;
+  if (!dr_plan(n_seg, H, dk, dvp, &L, &rpt)) return HK_ERR_UNSUPPORTED;
+  int e = hk_launch(mlstm_gates_kernel, dim3((unsigned)((n_seg * H + 63) / 64)), dim3(64), 0, s, il, fl, ld, i_bias, f_bias, segs,
+                    m_state, gates, n_seg, H, cap);
+  if (e) return e;
+  const long long items = (long long)n_rows * H;
+  e = hk_launch(mlstm_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, q, k, v, ld, (const float*)gates, rec, items,
+                H, dk, dv, dvp, L, rpt, q_scale);
+  if (e) return e;
+  return dr_scan_records(rec, segs, n_seg, state, out, H, dk, dvp, L, rpt, s);
+}
+
+// ------------------------------------------------------------------ the output of a head of a recurrent mixer
+// One warp per (token, head): y = N(o / den) * weight * act(g), narrowed to T.  N divides by the root mean square over the
+// head's dv values (eps inside the root).  o is read from rows of `ldo` floats per head (dv of them used).  `den`:
+// with gates != null the head's values are first divided by max(|o[dv]|, gates[item, 2]) + den_eps (the mLSTM's
+// normaliser: o[dv] is n . q, gates[.., 2] is e^(-m)).  The weight is [H, dv], or [dv] shared by the heads; act is the
+// logistic function or silu.
+template <typename T>
+__global__ void head_out_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, long long ldg,
+                                     const float* __restrict__ weight, int shared_weight, int act, const float* __restrict__ gates,
+                                     float den_eps, T* __restrict__ out, long long items, int H, int dv, float eps) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const long long t = item / H;
+  const int h = (int)(item % H);
+  const float* src = o + (size_t)item * ldo;
+  float scale = 1.0f;
+  if (gates != nullptr) scale = 1.0f / (fmaxf(fabsf(src[dv]), gates[item * 3 + 2]) + den_eps);
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) {
+    const float a = src[i] * scale;
+    ss = fmaf(a, a, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = scale / sqrtf(ss / (float)dv + eps);
+  const float* wp = weight + (shared_weight ? 0 : (size_t)h * dv);
+  for (int i = lane; i < dv; i += 32) {
+    const float gl = g[(size_t)t * ldg + (size_t)h * dv + i];
+    const float gate = act == 0 ? sigmoid_f(gl) : gl * sigmoid_f(gl);
+    out[(size_t)item * dv + i] = from_f32<T>(src[i] * inv * wp[i] * gate);
+  }
+}
+
+HK_API int hk_head_out_gate(const float* o, int ldo, const float* g, long long ldg, const float* weight, int shared_weight,
+                            int act, const float* gates, float den_eps, void* out, int out_dtype, int n, int H, int dv, float eps,
+                            void* stream) {
+  if (n <= 0) return 0;
+  if (ldo < dv || (gates != nullptr && ldo < dv + 1) || act < 0 || act > 1) return HK_ERR_UNSUPPORTED;
+  const long long items = (long long)n * H;
+  const unsigned blocks = (unsigned)((items + 7) / 8);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_dtype == HK_F32)
+    return hk_launch(head_out_gate_kernel<float>, dim3(blocks), dim3(256), 0, s, o, ldo, g, ldg, weight, shared_weight, act, gates,
+                     den_eps, (float*)out, items, H, dv, eps);
+  if (out_dtype == HK_BF16)
+    return hk_launch(head_out_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, s, o, ldo, g, ldg, weight, shared_weight, act, gates,
+                     den_eps, (bf16*)out, items, H, dv, eps);
   return HK_ERR_UNSUPPORTED;
 }

@@ -3,7 +3,9 @@
 `ModelSpec` holds the embedding, a list of blocks, the output head and a *schedule*: the
 list of layer calls of one forward pass.  A call names a layer of the list; the same layer
 may be named twice (shared weights, a cache of its own for each call), and a call may read
-the cache of an earlier call instead of keeping one (`cache_of`).  The default schedule
+the cache of an earlier call instead of keeping one (`cache_of`).  A call with `add_embedding`
+first adds the embedding's output (the residual stream as it was before the first layer) to the
+stream: a group of layers that runs several times sees the tokens again at every pass.  The default schedule
 runs every layer once in order, which is the reference's loop
 (src/engine/cpu_backend.zig:258).
 """
@@ -21,6 +23,7 @@ from ..parts.base import Part
 class LayerCall:
     layer: int
     cache_of: Optional[int] = None   # index (in the schedule) of an earlier call whose cache is read
+    add_embedding: bool = False      # the embedding's output is added to the residual stream before this call
 
 
 class ModelSpec(Part):
@@ -72,8 +75,15 @@ class ModelSpec(Part):
             self.embedding.forward(ctx.token_ids, x, ctx.residual_narrow)
         else:
             self.embedding.forward(ctx.token_ids, x)
+        x0 = None
+        if any(call.add_embedding for call in self.schedule):
+            x0 = x.clone()
         for ci, call in enumerate(self.schedule):
             own = call.cache_of is None
+            if call.add_embedding:
+                from ..csrc import ops
+                ops.scaled_sum(x, x0, 1.0)
+                ctx.residual_narrow = None          # nobody wrote the rounded copy of the new sum
             if not keeps[ci]:
                 ctx.residual_narrow = None
             self.layers[call.layer].forward(x, ctx, caches[ci if own else call.cache_of], write_cache=own)

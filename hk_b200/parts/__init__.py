@@ -6,11 +6,13 @@ from .embedding import OutputHead, TokenEmbedding
 from .feed_forward import PolyNormFeedForward, RoutedFeedForward, SwiGLUFeedForward
 from .latent_attention import LatentAttention
 from .norm import RMSNorm
+from .parallel import ParallelMixer
 from .position import RopeScaling, RotaryEmbedding
-from .recurrent import GeneralDeltaRule, MinGRU
+from .recurrent import GatedDeltaRule, GeneralDeltaRule, MLSTM, MinGRU
+from .side_input import TokenSideInput
 
 __all__ = [
-    "GQAAttention", "GeneralDeltaRule", "KVCacheSpec", "LatentAttention", "MinGRU", "PostNormBlock", "PolyNormFeedForward", "RoutedFeedForward", "SandwichNormBlock", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
+    "GQAAttention", "GatedDeltaRule", "GeneralDeltaRule", "MLSTM", "ParallelMixer", "TokenSideInput", "KVCacheSpec", "LatentAttention", "MinGRU", "PostNormBlock", "PolyNormFeedForward", "RoutedFeedForward", "SandwichNormBlock", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
     "RMSNorm", "RopeScaling", "RotaryEmbedding", "StateSpec", "StepTables", "SwiGLUFeedForward", "TABLE", "TokenEmbedding", "VECTOR",
     "part_class", "register_part",
 ]

@@ -164,7 +164,7 @@ class GQAAttention(Part):
             specs[p + nm["q_bias"]] = ParamSpec((H * hd,), VECTOR)
             specs[p + nm["k_bias"]] = ParamSpec((G * hd,), VECTOR)
             if not self.value_from_key:
-                specs[p + nm["v_bias"]] = ParamSpec((G * hd,), VECTOR)
+                specs[p + nm["v_bias"]] = ParamSpec((G * self.vd,), VECTOR)
         if self.o_bias:
             specs[p + nm["o_bias"]] = ParamSpec((d,), VECTOR)
         return specs

@@ -1,34 +1,43 @@
 """Arrangement of a layer's parts.  `PreNormBlock` is the reference's layer
 (src/engine/cpu_backend.zig:258-325): norm -> mixer -> residual sum -> norm -> feed-forward
 -> residual sum.  The residual stream is float32; the mixer and the feed-forward add onto
-it in place.  A block says which caches it keeps (`cache_specs()`, here the one of its mixer)
-and is handed exactly those, so a block with two mixers, or with none, is a block like any other."""
+it in place.  A block says which caches it keeps (`cache_specs()`, here those of its mixer)
+and is handed exactly those, so a block with two mixers, or with none, is a block like any other.
+`PreNormBlock` may go without a feed-forward, and may end with one more part that reads and changes the residual
+stream (`after`: a per-layer token input, for instance)."""
 from __future__ import annotations
 
 import torch
 
 from .base import Part, register_part
+from .parallel import mixer_cache_specs, mixer_caches
 
 
 class PreNormBlock(Part):
     graph_safe = True   # reads the batch from device tensors only
 
-    def __init__(self, mixer_norm, mixer, ffn_norm, feed_forward):
+    def __init__(self, mixer_norm, mixer, ffn_norm=None, feed_forward=None, after=None):
+        if (feed_forward is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is given")
         self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward = mixer_norm, mixer, ffn_norm, feed_forward
+        self.after = after          # forward(residual, ctx): one more sublayer behind the feed-forward
 
     def children(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward, self.after) if p is not None)
 
     def cache_specs(self):
-        """One cache: the mixer's."""
-        return [self.mixer.cache_spec()]
+        """The mixer's caches: one, or as many as it names."""
+        return mixer_cache_specs(self.mixer)
 
     def forward(self, residual: torch.Tensor, ctx, caches, write_cache: bool = True) -> None:
         xb = torch.empty(residual.shape, dtype=ctx.precision.compute, device=residual.device)
         self.mixer_norm.forward(residual, xb)
-        self.mixer.forward(xb, residual, ctx, caches[0], write_cache)
-        self.ffn_norm.forward(residual, xb)
-        self.feed_forward.forward(xb, residual, ctx)
+        self.mixer.forward(xb, residual, ctx, mixer_caches(self.mixer, caches), write_cache)
+        if self.feed_forward is not None:
+            self.ffn_norm.forward(residual, xb)
+            self.feed_forward.forward(xb, residual, ctx)
+        if self.after is not None:
+            self.after.forward(residual, ctx)
 
 
 register_part("block", "pre_norm", PreNormBlock)

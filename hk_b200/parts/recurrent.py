@@ -18,6 +18,25 @@ output is float32.
 `MinGRU` (one scalar state per channel, zero at the start; the gates read only the current token):
       z = sigmoid(W_z h + b_z);  x = W_x h + b_x;  c = x + 1/2 for x >= 0, sigmoid(x) below
       S <- (1 - z) S + z c;   y = W_o (S * silu(W_g h))
+
+`GatedDeltaRule` (per head a matrix state S [key_dim, value_dim], zero at the start; `kv_heads` query/key heads serve
+`n_heads` value heads, head h reading query/key head h // (n_heads / kv_heads)):
+      q, k, v = silu(conv(W_q h)), silu(conv(W_k h)), silu(conv(W_v h))     a short causal convolution per channel
+      q <- q / sqrt(sum(q^2) + unit_eps) * key_dim^(-1/2),   k <- k / sqrt(sum(k^2) + unit_eps)        per head
+      beta = sigmoid(W_b h),   g = exp(-exp(A_log) * softplus(W_a h + dt_bias))                      one per head
+      S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+      y = W_o ((o / rms(o) per head) * norm_weight[value_dim] * silu(W_g h))
+  The request's state is S and the last taps - 1 inputs of the convolution (two `StateSpec`s).
+
+`MLSTM` (per head a matrix S [key_dim, value_dim], a vector n [key_dim] and a running maximum m that starts at 0):
+      q = W_q h * key_dim^(-1/2), k = W_k h, v = W_v h
+      i = cap tanh((W_i h + b_i) / cap),   f = logsigmoid(cap tanh((W_f h + b_f) / cap))              one per head
+      m' = max(f + m, i);   S <- e^(f + m - m') S + e^(i - m') k v^T;   n <- e^(f + m - m') n + e^(i - m') k
+      o = S^T q / (max(|n . q|, e^(-m')) + den_eps)
+      y = W_o ((o / rms(o) per head) * norm_weight[n_heads * value_dim] * sigmoid(W_g h))
+  n is kept as one more column of S (its value is always 1), m in a `StateSpec` of its own.
+
+A mixer with several caches says so with `cache_specs()` and is handed the list.
 """
 from __future__ import annotations
 
@@ -155,5 +174,129 @@ class MinGRU(_SegmentScan):
         ops.gemm(out, self.w_o, residual, accumulate=accumulate)
 
 
+class GatedDeltaRule(_SegmentScan):
+    def __init__(self, hidden: int, n_heads: int, kv_heads: int, key_dim: int, value_dim: int, taps: int, prefix: str,
+                 norm_eps: float, unit_eps: float = 1e-6, q_scale: Optional[float] = None, out_scale: float = 1.0,
+                 names: Optional[Dict[str, str]] = None):
+        if n_heads % kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {kv_heads} query/key heads")
+        if taps < 2:
+            raise ValueError("the short convolution needs at least two taps")
+        self.hidden, self.H, self.G, self.dk, self.dv, self.taps = hidden, n_heads, kv_heads, key_dim, value_dim, int(taps)
+        self.prefix, self.norm_eps, self.unit_eps = prefix, float(norm_eps), float(unit_eps)
+        self.q_scale = float(q_scale) if q_scale is not None else key_dim ** -0.5
+        self.out_scale = float(out_scale)      # a factor on the mixer's result (carried by the output norm's weight)
+        self.names = {"q": "q", "k": "k", "v": "v", "q_conv": "q.conv", "k_conv": "k.conv", "v_conv": "v.conv", "b": "b",
+                      "a": "a", "a_log": "A_log", "dt_bias": "dt_bias", "g": "g", "norm": "norm", "o": "o"}
+        self.names.update(names or {})
+        self.w_in = self.w_o = self.conv = self.a_log = self.dt_bias = self.norm_weight = None
+
+    @property
+    def channels(self) -> int:
+        return 2 * self.G * self.dk + self.H * self.dv
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        p, nm, d = self.prefix, self.names, self.hidden
+        K, V = self.G * self.dk, self.H * self.dv
+        return {
+            p + nm["q"]: ParamSpec((K, d), MATRIX), p + nm["k"]: ParamSpec((K, d), MATRIX),
+            p + nm["v"]: ParamSpec((V, d), MATRIX), p + nm["g"]: ParamSpec((V, d), MATRIX),
+            p + nm["q_conv"]: ParamSpec((K, self.taps), VECTOR), p + nm["k_conv"]: ParamSpec((K, self.taps), VECTOR),
+            p + nm["v_conv"]: ParamSpec((V, self.taps), VECTOR),
+            p + nm["b"]: ParamSpec((self.H, d), MATRIX), p + nm["a"]: ParamSpec((self.H, d), MATRIX),
+            p + nm["a_log"]: ParamSpec((self.H,), VECTOR), p + nm["dt_bias"]: ParamSpec((self.H,), VECTOR),
+            p + nm["norm"]: ParamSpec((self.dv,), VECTOR, "one_plus_normal"), p + nm["o"]: ParamSpec((d, V), MATRIX),
+        }
+
+    def cache_specs(self):
+        return [StateSpec((self.H, self.dk, self.dv), torch.float32), StateSpec((self.taps - 1, self.channels), torch.float32)]
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        p, nm = self.prefix, self.names
+        mats = [tensors[p + nm[c]] for c in ("q", "k", "v", "g", "b", "a")]
+        wide = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        # one product gives the convolutions' inputs, the output gate's logits and the two per-head logits
+        self.w_in = torch.cat([t.to(wide) for t in mats], dim=0).contiguous()
+        self.conv = torch.cat([tensors[p + nm[c]] for c in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        self.w_o = tensors[p + nm["o"]]
+        self.a_log, self.dt_bias = tensors[p + nm["a_log"]], tensors[p + nm["dt_bias"]]
+        self.norm_weight = tensors[p + nm["norm"]]
+        if self.out_scale != 1.0:
+            self.norm_weight = (self.norm_weight * self.out_scale).contiguous()
+
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
+                accumulate: bool = True) -> None:
+        n = xb.shape[0]
+        K, V, C, H = self.G * self.dk, self.H * self.dv, self.channels, self.H
+        state, tail = cache[0].state, cache[1].state
+        segs = self._segments(ctx)
+        proj = torch.empty((n, self.w_in.shape[0]), dtype=torch.float32, device=xb.device)
+        ops.gemm(xb, self.w_in, proj)
+        act = torch.empty((n, C), dtype=torch.float32, device=xb.device)
+        ops.short_conv(proj[:, :C], self.conv, segs, tail, act)
+        o = torch.empty((n, V), dtype=torch.float32, device=xb.device)
+        ops.gated_delta_scan(act[:, :K], act[:, K:2 * K], act[:, 2 * K:], proj[:, C + V:C + V + H], proj[:, C + V + H:],
+                             self.a_log, self.dt_bias, segs, state, o, H, self.G, self.dk, self.dv, self.q_scale, self.unit_eps)
+        og = torch.empty((n, V), dtype=xb.dtype, device=xb.device)
+        ops.head_out_gate(o, proj[:, C:C + V], self.norm_weight, self.norm_eps, og, H, self.dv, act="silu")
+        ops.gemm(og, self.w_o, residual, accumulate=accumulate)
+
+
+class MLSTM(_SegmentScan):
+    def __init__(self, hidden: int, n_heads: int, key_dim: int, value_dim: int, gate_cap: float, prefix: str, norm_eps: float,
+                 den_eps: float = 1e-6, q_scale: Optional[float] = None, names: Optional[Dict[str, str]] = None):
+        if not gate_cap > 0:
+            raise ValueError("the gates' cap must be positive")
+        self.hidden, self.H, self.dk, self.dv = hidden, n_heads, key_dim, value_dim
+        self.dvp = ops.mlstm_padded(value_dim)
+        self.cap, self.prefix, self.norm_eps, self.den_eps = float(gate_cap), prefix, float(norm_eps), float(den_eps)
+        self.q_scale = float(q_scale) if q_scale is not None else key_dim ** -0.5
+        self.names = {"q": "q", "k": "k", "v": "v", "g": "g", "i": "i", "i_bias": "i.b", "f": "f", "f_bias": "f.b",
+                      "norm": "norm", "o": "o"}
+        self.names.update(names or {})
+        self.w_in = self.w_o = self.i_bias = self.f_bias = self.norm_weight = None
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        p, nm, d = self.prefix, self.names, self.hidden
+        K, V, H = self.H * self.dk, self.H * self.dv, self.H
+        return {
+            p + nm["q"]: ParamSpec((K, d), MATRIX), p + nm["k"]: ParamSpec((K, d), MATRIX),
+            p + nm["v"]: ParamSpec((V, d), MATRIX), p + nm["g"]: ParamSpec((V, d), MATRIX),
+            p + nm["i"]: ParamSpec((H, d), MATRIX), p + nm["i_bias"]: ParamSpec((H,), VECTOR),
+            p + nm["f"]: ParamSpec((H, d), MATRIX), p + nm["f_bias"]: ParamSpec((H,), VECTOR),
+            p + nm["norm"]: ParamSpec((V,), VECTOR, "one_plus_normal"), p + nm["o"]: ParamSpec((d, V), MATRIX),
+        }
+
+    def cache_specs(self):
+        return [StateSpec((self.H, self.dk, self.dvp), torch.float32), StateSpec((self.H,), torch.float32)]
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        p, nm = self.prefix, self.names
+        mats = [tensors[p + nm[c]] for c in ("q", "k", "v", "g", "i", "f")]
+        wide = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.w_in = torch.cat([t.to(wide) for t in mats], dim=0).contiguous()
+        self.w_o = tensors[p + nm["o"]]
+        self.i_bias, self.f_bias = tensors[p + nm["i_bias"]], tensors[p + nm["f_bias"]]
+        self.norm_weight = tensors[p + nm["norm"]]
+
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
+                accumulate: bool = True) -> None:
+        n = xb.shape[0]
+        K, V, H = self.H * self.dk, self.H * self.dv, self.H
+        proj = torch.empty((n, self.w_in.shape[0]), dtype=torch.float32, device=xb.device)
+        ops.gemm(xb, self.w_in, proj)
+        o = torch.empty((n, H * self.dvp), dtype=torch.float32, device=xb.device)
+        gates = torch.empty((n, H, 3), dtype=torch.float32, device=xb.device)
+        ops.mlstm_scan(proj[:, :K], proj[:, K:2 * K], proj[:, 2 * K:2 * K + V], proj[:, 2 * K + 2 * V:2 * K + 2 * V + H],
+                       proj[:, 2 * K + 2 * V + H:], self.i_bias, self.f_bias, self._segments(ctx), cache[0].state,
+                       cache[1].state, o, gates, H, self.dk, self.dv, self.cap, self.q_scale)
+        og = torch.empty((n, V), dtype=xb.dtype, device=xb.device)
+        ops.head_out_gate(o, proj[:, 2 * K + V:2 * K + 2 * V], self.norm_weight, self.norm_eps, og, H, self.dv, act="sigmoid",
+                          gates=gates, den_eps=self.den_eps)
+        ops.gemm(og, self.w_o, residual, accumulate=accumulate)
+
+
 register_part("mixer", "general_delta_rule", GeneralDeltaRule)
+register_part("mixer", "gated_delta_rule", GatedDeltaRule)
+register_part("mixer", "mlstm", MLSTM)
 register_part("mixer", "mingru", MinGRU)
