@@ -31,6 +31,10 @@ class ParallelMixer(Part):
         self.left_scale, self.right_scale = float(left_scale), float(right_scale)
         self._n_left = len(mixer_cache_specs(left))
 
+    @property
+    def hidden(self) -> int:
+        return self.left.hidden
+
     def children(self):
         return (self.left, self.right)
 

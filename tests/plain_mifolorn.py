@@ -9,6 +9,14 @@ import math
 
 import numpy as np
 
+round_inputs = None      # a function that rounds an array as the serving engine's storage type does, or None
+
+
+def product(h, weight):
+    """h W^T; with `round_inputs` set, the rows are rounded first: a coarse model of what 16-bit inputs of the
+    products do, by which the tests know how far rounding alone moves the logits of a position."""
+    return (round_inputs(h) if round_inputs is not None else h) @ weight.T
+
 
 def rms(x, eps):
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
@@ -77,13 +85,15 @@ def softmax_attention(h, w, p, m, eps):
     T = h.shape[0]
     H, G, dk = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"])
     dv = int(m.get("vdim", dk))
-    q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, dk)
-    k = (h @ w[p + "k"].T + w[p + "k.b"]).reshape(T, G, dk)
-    v = (h @ w[p + "v"].T + w[p + "v.b"]).reshape(T, G, dv)
+    q = (product(h, w[p + "q"]) + w[p + "q.b"]).reshape(T, H, dk)
+    k = (product(h, w[p + "k"]) + w[p + "k.b"]).reshape(T, G, dk)
+    v = (product(h, w[p + "v"]) + w[p + "v.b"]).reshape(T, G, dv)
     q = rms(q, eps) * w[p + "q.norm"]
     k = rms(k, eps) * w[p + "k.norm"]
     pos = np.arange(T)
     q, k = rotate(q, pos, m.get("rot")), rotate(k, pos, m.get("rot"))
+    if round_inputs is not None:               # the cache and the queries are kept in the storage type
+        q, k, v = round_inputs(q), round_inputs(k), round_inputs(v)
     cap = m.get("softcap")
     out = np.zeros((T, H, dv))
     for hh in range(H):
@@ -95,8 +105,8 @@ def softmax_attention(h, w, p, m, eps):
         s = s - s.max(axis=1, keepdims=True)
         e = np.exp(s)
         out[:, hh] = (e / e.sum(axis=1, keepdims=True)) @ v[:, g]
-    y = out.reshape(T, H * dv) * sigmoid(h @ w[p + "g"].T)
-    return y @ w[p + "o"].T
+    y = out.reshape(T, H * dv) * sigmoid(product(h, w[p + "g"]))
+    return product(y, w[p + "o"])
 
 
 def short_conv(x, taps_weight):
@@ -114,13 +124,13 @@ def short_conv(x, taps_weight):
 def gated_delta(h, w, p, m, eps):
     T = h.shape[0]
     H, G, dk, dv = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"])
-    q = silu(short_conv(h @ w[p + "q"].T, w[p + "q.conv"])).reshape(T, G, dk)
-    k = silu(short_conv(h @ w[p + "k"].T, w[p + "k.conv"])).reshape(T, G, dk)
-    v = silu(short_conv(h @ w[p + "v"].T, w[p + "v.conv"])).reshape(T, H, dv)
+    q = silu(short_conv(product(h, w[p + "q"]), w[p + "q.conv"])).reshape(T, G, dk)
+    k = silu(short_conv(product(h, w[p + "k"]), w[p + "k.conv"])).reshape(T, G, dk)
+    v = silu(short_conv(product(h, w[p + "v"]), w[p + "v.conv"])).reshape(T, H, dv)
     q = q / np.sqrt(np.sum(q * q, axis=-1, keepdims=True) + 1e-6) * dk ** -0.5
     k = k / np.sqrt(np.sum(k * k, axis=-1, keepdims=True) + 1e-6)
-    beta = sigmoid(h @ w[p + "b"].T)                                             # [T, H]
-    decay = np.exp(-np.exp(w[p + "A_log"]) * softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))
+    beta = sigmoid(product(h, w[p + "b"]))                                             # [T, H]
+    decay = np.exp(-np.exp(w[p + "A_log"]) * softplus(product(h, w[p + "a"]) + w[p + "dt_bias"]))
     out = np.zeros((T, H, dv))
     for hh in range(H):
         g = hh // (H // G)
@@ -130,18 +140,18 @@ def gated_delta(h, w, p, m, eps):
             u = beta[t, hh] * (v[t, hh] - S.T @ k[t, g])
             S = S + np.outer(k[t, g], u)
             out[t, hh] = S.T @ q[t, g]
-    y = rms(out, eps) * w[p + "norm"] * silu(h @ w[p + "g"].T).reshape(T, H, dv)
-    return y.reshape(T, H * dv) @ w[p + "o"].T
+    y = rms(out, eps) * w[p + "norm"] * silu(product(h, w[p + "g"])).reshape(T, H, dv)
+    return product(y.reshape(T, H * dv), w[p + "o"])
 
 
 def mlstm(h, w, p, m, eps):
     T = h.shape[0]
     H, dk, dv, cap = int(m["heads"]), int(m["dim"]), int(m["vdim"]), float(m["gate_cap"])
-    q = (h @ w[p + "q"].T).reshape(T, H, dk) * dk ** -0.5
-    k = (h @ w[p + "k"].T).reshape(T, H, dk)
-    v = (h @ w[p + "v"].T).reshape(T, H, dv)
-    ig = cap * np.tanh((h @ w[p + "i"].T + w[p + "i.b"]) / cap)
-    fg = logsigmoid(cap * np.tanh((h @ w[p + "f"].T + w[p + "f.b"]) / cap))
+    q = (product(h, w[p + "q"])).reshape(T, H, dk) * dk ** -0.5
+    k = (product(h, w[p + "k"])).reshape(T, H, dk)
+    v = (product(h, w[p + "v"])).reshape(T, H, dv)
+    ig = cap * np.tanh((product(h, w[p + "i"]) + w[p + "i.b"]) / cap)
+    fg = logsigmoid(cap * np.tanh((product(h, w[p + "f"]) + w[p + "f.b"]) / cap))
     out = np.zeros((T, H, dv))
     for hh in range(H):
         S, nrm, mx = np.zeros((dk, dv)), np.zeros(dk), 0.0
@@ -152,8 +162,8 @@ def mlstm(h, w, p, m, eps):
             nrm = keep * nrm + take * k[t, hh]
             mx = new
             out[t, hh] = S.T @ q[t, hh] / (max(abs(nrm @ q[t, hh]), math.exp(-mx)) + 1e-6)
-    y = rms(out, eps).reshape(T, H * dv) * w[p + "norm"] * sigmoid(h @ w[p + "g"].T)
-    return y @ w[p + "o"].T
+    y = rms(out, eps).reshape(T, H * dv) * w[p + "norm"] * sigmoid(product(h, w[p + "g"]))
+    return product(y, w[p + "o"])
 
 
 def parallel(h, w, p, m, eps):
@@ -167,13 +177,13 @@ MIXERS = {"mlstm": mlstm, "delta": gated_delta, "parallel": parallel}
 # ---- the rest of a layer -----------------------------------------------------------------------------------------
 
 def feed_forward(h, w, p):
-    return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
+    return product(silu(product(h, w[p + "gate"])) * product(h, w[p + "up"]), w[p + "down"])
 
 
 def token_side_input(x, tokens, w, i, dim, eps):
     """What layer i adds from its own slice of the second embedding table."""
     e = w["side.embed"][np.asarray(tokens)][:, i * dim:(i + 1) * dim]
-    y = (gelu_tanh(x @ w[f"l{i}.side.gate"].T) * e) @ w[f"l{i}.side.proj"].T
+    y = product(gelu_tanh(product(x, w[f"l{i}.side.gate"])) * e, w[f"l{i}.side.proj"])
     return rms(y, eps) * w[f"l{i}.side.norm"]
 
 
@@ -214,4 +224,4 @@ def forward(cfg, w, tokens, trace=None):
         x = layer(x, tokens, w, cfg, i)
         if trace is not None:
             trace.append(x.copy())
-    return (rms(x, float(cfg["norm"]["eps"])) * w["final.norm"]) @ w["embed"].T
+    return product(rms(x, float(cfg["norm"]["eps"])) * w["final.norm"], w["embed"])
