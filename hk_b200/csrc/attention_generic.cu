@@ -17,7 +17,7 @@
 //   v_stride    elements between the values of consecutive tokens of a page; when it is not vd the values lie inside
 //               wider rows: a cache that keeps ONE tensor per token whose first vd dims are the value (v_pages = k_pages,
 //               v_stride = hd);
-//   gate        fp32 logits [n, gate_ld >= H * vd]: the output is multiplied by sigmoid(gate[t, h * vd + d]).
+//   gate        fp32 logits [n, gate_ld >= H * vd]: the output is multiplied by gate_scale * sigmoid(gate[t, h * vd + d]).
 //
 // Reference counterpart: `attention`, src/cuda_device.zig:1494-1594 (block per (token, head),
 // warp per position, online softmax); scale on q first: src/engine/attention_kernel.zig:109.
@@ -34,6 +34,7 @@ struct AgOptions {
   const float* sinks;
   const float* gate;
   long long gate_ld;
+  float gate_scale;
 };
 
 // AG_MAX_PER_LANE: dims per lane, 8 for widths up to 256, 20 up to 640
@@ -119,7 +120,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 #pragma unroll
     for (int w = 0; w < AG_WARPS; ++w) a += acc_s[w * vd + d] * f[w];
     a /= lt;
-    if (opt.gate) a /= 1.0f + expf(-opt.gate[(size_t)t * opt.gate_ld + (size_t)h * vd + d]);
+    if (opt.gate) a = a * opt.gate_scale / (1.0f + expf(-opt.gate[(size_t)t * opt.gate_ld + (size_t)h * vd + d]));
     op[d] = from_f32<T>(a);
   }
 }
@@ -140,12 +141,12 @@ HK_API int hk_attention_generic(const void* q, const void* k_pages, const void* 
                                 const int* block_table, int table_stride, const int* positions,
                                 const int* slot_of_token, void* out, int n, int H, int G, int hd,
                                 int page_tokens, int window, float scale, int vd, int sink, const float* sinks, float softcap,
-                                int chunk, int v_stride, const float* gate, long long gate_ld, void* stream) {
+                                int chunk, int v_stride, const float* gate, long long gate_ld, float gate_scale, void* stream) {
   if (n <= 0) return 0;
   const int widest = hd > vd ? hd : vd;
   if (widest > 640 || hd < 1 || G < 1 || H % G != 0 || vd < 1 || v_stride < vd || softcap < 0.f || chunk < 0) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-  AgOptions opt = {softcap, chunk, v_stride, sinks, gate, gate_ld};
+  AgOptions opt = {softcap, chunk, v_stride, sinks, gate, gate_ld, gate_scale};
   if (dtype != HK_F32 && dtype != HK_BF16) return HK_ERR_UNSUPPORTED;
 #define AG_GO(T, PER) ag_launch<T, PER>(q, k_pages, v_pages, block_table, table_stride, positions, slot_of_token, out, n, H, G, hd, \
                                         page_tokens, window, scale, vd, sink, opt, s)

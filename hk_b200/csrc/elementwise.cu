@@ -783,11 +783,11 @@ HK_API int hk_tanh_cols(const float* x, long long ld, void* out, int out_dtype, 
 }
 
 // ----------------------------------------------------------------------------- output gate of a mixer
-// out[t, j] = x[t, j] * sigmoid(gate[t, j]) for x [n, W] (fp32, or the storage type) and the gate's logits as a column
+// out[t, j] = x[t, j] * scale * sigmoid(gate[t, j]) for x [n, W] (fp32, or the storage type) and the gate's logits as a column
 // slice of a fused projection's fp32 output (row stride ld).
 template <typename TI, typename TO>
 __global__ void sigmoid_gate_kernel(const TI* __restrict__ x, const float* __restrict__ gate, long long ld, TO* __restrict__ out,
-                                    long long total, int W) {
+                                    long long total, int W, float scale) {
   pdl_launch_dependents();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -795,21 +795,21 @@ __global__ void sigmoid_gate_kernel(const TI* __restrict__ x, const float* __res
   const long long t = i / W;
   const int j = (int)(i % W);
   const float g = gate[t * ld + j];
-  out[i] = from_f32<TO>(to_f32<TI>(x[i]) / (1.0f + expf(-g)));
+  out[i] = from_f32<TO>(to_f32<TI>(x[i]) * scale / (1.0f + expf(-g)));
 }
 
 HK_API int hk_sigmoid_gate(const void* x, int x_dtype, const float* gate, long long ld, void* out, int out_dtype, int n, int W,
-                           void* stream) {
+                           float scale, void* stream) {
   if (n <= 0 || W <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const long long total = (long long)n * W;
   const dim3 grid((unsigned)((total + 255) / 256)), block(256);
   if (x_dtype == HK_F32 && out_dtype == HK_F32)
-    return hk_launch(sigmoid_gate_kernel<float, float>, grid, block, 0, s, (const float*)x, gate, ld, (float*)out, total, W);
+    return hk_launch(sigmoid_gate_kernel<float, float>, grid, block, 0, s, (const float*)x, gate, ld, (float*)out, total, W, scale);
   if (x_dtype == HK_F32 && out_dtype == HK_BF16)
-    return hk_launch(sigmoid_gate_kernel<float, bf16>, grid, block, 0, s, (const float*)x, gate, ld, (bf16*)out, total, W);
+    return hk_launch(sigmoid_gate_kernel<float, bf16>, grid, block, 0, s, (const float*)x, gate, ld, (bf16*)out, total, W, scale);
   if (x_dtype == HK_BF16 && out_dtype == HK_BF16)
-    return hk_launch(sigmoid_gate_kernel<bf16, bf16>, grid, block, 0, s, (const bf16*)x, gate, ld, (bf16*)out, total, W);
+    return hk_launch(sigmoid_gate_kernel<bf16, bf16>, grid, block, 0, s, (const bf16*)x, gate, ld, (bf16*)out, total, W, scale);
   return HK_ERR_UNSUPPORTED;
 }
 

@@ -323,7 +323,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool =
 
 def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, out, n_heads, n_kv_heads,
                     head_dim, page_tokens, window: int, scale: float, plan=None, sink: bool = False, sinks=None,
-                    softcap: float = 0.0, chunk: int = 0, gate=None) -> None:
+                    softcap: float = 0.0, chunk: int = 0, gate=None, gate_scale: float = 1.0) -> None:
     """out[t, h, :] = softmax_j(scale * q[t, h] . k[j]) v[j] over the keys j in
     [max(0, p - window + 1), p] (all of [0, p] when window <= 0) of the token's request, read
     through its block-table row; p = positions[t].  `plan` carries the per-request tiling the
@@ -334,7 +334,7 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
     that float32 [H] tensor is given: p_j = exp(s_j) / (exp(sink) + sum exp(s_j)).
     `softcap` c > 0: scores become c * tanh(score / c).  `chunk` s > 0: a token sees no key before the start of its own
     block of s positions.  `gate` (a float32 column slice [n, H*vd] of a projection's output): the result is
-    multiplied by sigmoid(gate)."""
+    multiplied by gate_scale * sigmoid(gate)."""
     _need(q, "q", dims=2)
     _need(out, "out", q.dtype, 2)
     _need(k_pages, "k_pages", q.dtype, 4)
@@ -370,7 +370,7 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
         if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan,
                               allow_tma=choice != "flash_cp", sink=sink, sinks=sinks, softcap=softcap, chunk=chunk):
             if gate is not None:
-                sigmoid_gate(out, gate, out)
+                sigmoid_gate(out, gate, out, gate_scale)
             return
         if choice is not None:
             raise KernelError(f"paged_attention: the '{choice}' kernel refuses head_dim={hd} page_tokens={page_tokens}")
@@ -379,11 +379,12 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
         _ptr(q), _ptr(k_pages), _ptr(v_pages if v_pages is not None else k_pages), _dt(q), _ptr(block_table),
         int(block_table.shape[1]), _ptr(positions), _ptr(slot_of_token), _ptr(out), n, H, G, hd, int(page_tokens), int(window),
         ctypes.c_float(scale), vd, 1 if sink else 0, _ptr(sinks), ctypes.c_float(softcap), int(chunk),
-        vd if v_pages is not None else hd, _ptr(gate), ctypes.c_longlong(gate_ld), _stream()), "paged_attention")
+        vd if v_pages is not None else hd, _ptr(gate), ctypes.c_longlong(gate_ld), ctypes.c_float(gate_scale), _stream()),
+        "paged_attention")
 
 
-def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
-    """out = x * sigmoid(gate) element by element; x [n, W] float32 or out's type, gate a float32 column slice [n, W] of
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out = x * scale * sigmoid(gate) element by element; x [n, W] float32 or out's type, gate a float32 column slice [n, W] of
     a projection's output (any row stride)."""
     _need(x, "x", dims=2)
     _need(out, "out", dims=2)
@@ -392,8 +393,8 @@ def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None
     if x.shape != out.shape or gate.shape[0] != n or (x.dtype != torch.float32 and x.dtype != out.dtype):
         raise KernelError("sigmoid_gate: shapes or types do not fit")
     lib = build.load("elementwise")
-    _check(lib.hk_sigmoid_gate(_ptr(x), _dt(x), _ptr(gate), ctypes.c_longlong(ld), _ptr(out), _dt(out), n, W, _stream()),
-           "sigmoid_gate")
+    _check(lib.hk_sigmoid_gate(_ptr(x), _dt(x), _ptr(gate), ctypes.c_longlong(ld), _ptr(out), _dt(out), n, W, ctypes.c_float(scale),
+                               _stream()), "sigmoid_gate")
 
 
 def latent_prep(proj, q_plain, q_full, c_weight, eps, cos, sin, rotary_dim, pairing, positions, slot_of_token, block_table,

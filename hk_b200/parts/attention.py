@@ -28,7 +28,8 @@ Further parameters, for designs other than the reference's:
   `chunk` s cuts the sequence into blocks of s positions counted from position 0: a token sees the keys of its own
   block up to itself and none of an earlier block;
   `gate` multiplies the concatenated heads' outputs, before W_o, element by element with sigmoid(W_g x) of the
-  mixer's own input (tensor `g` [H * v_head_dim, hidden], fused into the q/k/v product);
+  mixer's own input (tensor `g` [H * v_head_dim, hidden], fused into the q/k/v product); `out_scale` is a factor on
+  the mixer's result that the gate carries;
   `names` renames the tensors (keys q, k, v, o, q_norm, k_norm, sink, gate, and q_bias, k_bias, v_bias, o_bias).
 """
 from __future__ import annotations
@@ -90,7 +91,7 @@ class GQAAttention(Part):
                  o_bias: bool = False, qk_norm_after: bool = False, qk_norm_weight: bool = True,
                  value_from_key: bool = False, v_head_dim: Optional[int] = None, sink: bool = False,
                  names: Optional[Dict[str, str]] = None, sink_weights: bool = False, softcap: Optional[float] = None,
-                 chunk: Optional[int] = None, gate: bool = False):
+                 chunk: Optional[int] = None, gate: bool = False, out_scale: float = 1.0):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
         if head_dim > 256 or head_dim < 2:
@@ -104,6 +105,9 @@ class GQAAttention(Part):
         if sink_weights and not sink:
             raise ValueError("sink_weights needs sink")
         self.sink_weights, self.gate = bool(sink_weights), bool(gate)
+        if out_scale != 1.0 and not gate:
+            raise ValueError("out_scale rides on the output gate: it needs gate=True")
+        self.out_scale = float(out_scale)      # a factor on the mixer's result (carried by the output gate)
         self.softcap = float(softcap) if softcap else 0.0
         self.chunk = int(chunk) if chunk else 0
         if self.softcap < 0 or self.chunk < 0:
@@ -236,7 +240,8 @@ class GQAAttention(Part):
         att = torch.empty((n, H * self.vd), dtype=xb.dtype, device=xb.device)
         ops.paged_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.slot_of_token,
                             att, H, G, hd, cache.page_tokens, self.window or 0, self.scale,
-                            plan=plan, sink=self.sink, sinks=self.sinks, softcap=self.softcap, chunk=self.chunk, gate=gate)
+                            plan=plan, sink=self.sink, sinks=self.sinks, softcap=self.softcap, chunk=self.chunk, gate=gate,
+                            gate_scale=self.out_scale)
         ops.gemm(att, self.w_o, residual, accumulate=accumulate, bias=self.b_o)
 
 

@@ -1,8 +1,11 @@
 """Two mixers side by side: both read the same input, and the layer receives
     left_scale * left(h) + right_scale * right(h).
 Either side is any mixer part (an attention over pages beside a recurrent mixer with a state, for instance); the
-pair keeps the caches of both, the left one's first.  Each side stores its float32 result in a buffer of its own
-and one kernel adds both, with their factors, onto the residual stream, so the sum is taken in 32-bit."""
+pair keeps the caches of both, the left one's first.  A side that can carry a factor on its result (it has a
+settable `out_scale`: an attention's output gate, a recurrent mixer's output norm) is given its factor when the pair
+is made, and then both sides add their output projection straight onto the float32 residual stream.  Otherwise
+each side stores its float32 result in a buffer of its own and one kernel adds both, with their factors, onto the
+residual stream.  Either way the sum is taken in 32-bit."""
 from __future__ import annotations
 
 import torch
@@ -23,6 +26,11 @@ def mixer_caches(mixer, caches):
     return list(caches) if hasattr(mixer, "cache_specs") else caches[0]
 
 
+def _takes_scale(mixer) -> bool:
+    """Whether the mixer carries a factor on its result by itself (set before its tensors are bound)."""
+    return hasattr(mixer, "out_scale") and bool(getattr(mixer, "gate", True))      # an attention carries it on its gate
+
+
 class ParallelMixer(Part):
     graph_safe = True   # reads the batch from device tensors only
 
@@ -30,6 +38,9 @@ class ParallelMixer(Part):
         self.left, self.right = left, right
         self.left_scale, self.right_scale = float(left_scale), float(right_scale)
         self._n_left = len(mixer_cache_specs(left))
+        self._carried = all(_takes_scale(m) for m in (left, right))
+        if self._carried:
+            left.out_scale, right.out_scale = self.left_scale, self.right_scale
 
     @property
     def hidden(self) -> int:
@@ -43,6 +54,10 @@ class ParallelMixer(Part):
 
     def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
                 accumulate: bool = True) -> None:
+        if self._carried:
+            self.left.forward(xb, residual, ctx, mixer_caches(self.left, cache[:self._n_left]), write_cache, accumulate=accumulate)
+            self.right.forward(xb, residual, ctx, mixer_caches(self.right, cache[self._n_left:]), write_cache, accumulate=True)
+            return
         y_left = torch.empty(residual.shape, dtype=torch.float32, device=residual.device)
         y_right = torch.empty_like(y_left)
         self.left.forward(xb, y_left, ctx, mixer_caches(self.left, cache[:self._n_left]), write_cache, accumulate=False)

@@ -279,6 +279,20 @@ def test_parallel_mixer_under_every_cut(dtype, which):
     under_every_cut(part, prec, dtype, {"a": 37, "b": 9, "c": 64}, lambda x: P.parallel(x, w, "m.", m, 1e-5))
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_parallel_mixer_whose_sides_carry_no_factor(dtype):
+    """A matrix memory on the right has no place for a factor on its result: both sides then write buffers of their
+    own and one kernel sums them with the factors."""
+    from hk_b200.parts import MLSTM, ParallelMixer
+    d, left = 48, LEFTS[0]
+    right = {"heads": 2, "dim": 16, "vdim": 8, "gate_cap": 8.0}
+    part = ParallelMixer(left_part(d, left, 1e-5), MLSTM(d, 2, 16, 8, 8.0, "m.right.", norm_eps=1e-5), 0.6, -1.4)
+    assert part.left.out_scale == 1.0
+    prec, w = bind_random(part, dtype, std=0.3)
+    under_every_cut(part, prec, dtype, {"a": 37, "b": 9, "c": 64},
+                    lambda x: 0.6 * P.softmax_attention(x, w, "m.left.", left, 1e-5) - 1.4 * P.mlstm(x, w, "m.right.", right, 1e-5))
+
+
 # ------------------------------------------------------------------------------------ per-layer token input, sums
 
 

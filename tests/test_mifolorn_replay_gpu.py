@@ -15,10 +15,16 @@ import mifolorn_models as M
 import plain_mifolorn as P
 from test_replay_gpu import families
 
-# (largest, mean) |difference| relative to the largest |logit|.  bfloat16: these models run their layers two or three
-# times and norm every head of the recurrent mixers' small outputs, which carries rounding further than a plain decoder
-# of the same depth does (3 % where those keep within 2 %); a fault is ten times larger.
-TOL = {torch.float32: (2e-5, 2e-6), torch.bfloat16: (3e-2, 4e-3)}
+# float32: (largest, mean) |difference| relative to the largest |logit|.
+TOL32 = (2e-5, 2e-6)
+# bfloat16: a position's error is the root mean square over the vocabulary of the difference (its mean taken off) relative
+# to that of the plain logits, and it is held against what rounding alone does at the same position (`rounding_alone`).
+# These models run their layers two or three times and norm every head of the recurrent mixers' small outputs, so a head
+# whose output is near zero before its norm amplifies rounding at single positions: the engine's error may be up to
+# SINGLE times the model's there (the largest seen is 6), at most OVER_SHARE of the positions may be beyond OVER times
+# it, and the median of the ratio stays below MEDIAN.  A lost key, state or tap moves every later position by several
+# tenths, tens of times what rounding does.
+FLOOR, SINGLE, OVER, OVER_SHARE, MEDIAN = 2e-3, 10.0, 3.0, 0.05, 1.5
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.join(os.path.dirname(os.path.abspath(__file__)), os.pardir)
@@ -46,38 +52,47 @@ def to_bfloat16(x):
     return torch.from_numpy(np.ascontiguousarray(x)).to(torch.bfloat16).double().numpy()
 
 
+def centred_rms(x):
+    x = x - x.mean(axis=-1, keepdims=True)
+    return np.sqrt((x * x).mean(axis=-1))
+
+
 def rounding_alone(cfg, weights, seqs, ref):
     """What rounding alone does to the plain logits, per request and position (by a coarse model: the inputs of the
-    matrix products, the queries and the cache narrowed, nothing else)."""
+    matrix products, the queries and the cache narrowed, nothing else), as a centred root mean square."""
     P.round_inputs = to_bfloat16
     try:
-        return {rid: np.abs(P.forward(cfg, weights, ids) - ref[rid]).max(axis=1) for rid, ids in seqs.items()}
+        return {rid: centred_rms(P.forward(cfg, weights, ids) - ref[rid]) for rid, ids in seqs.items()}
     finally:
         P.round_inputs = None
 
 
 def compare(got, ref, seqs, dtype, slack=None):
-    """Every position against the plain logits: max and mean |difference| relative to the largest |logit|; the FIRST
-    position out of tolerance is reported, since its place says what is special about it.  In bfloat16 the limit at a
-    position is the larger of the engine-wide one and four times what rounding alone does there (`slack`): a head
-    whose output is near zero before its norm amplifies rounding; a fault (a lost key or state) is ten times larger."""
+    """Every position against the plain logits; the FIRST position out of tolerance is reported, since its place says
+    what is special about it."""
     assert len(got) == sum(len(v) for v in seqs.values())
-    scale = max(np.abs(r).max() for r in ref.values())
-    tol_max, tol_mean = TOL[dtype]
-    means = []
-    for (rid, p), v in sorted(got.items()):
+    for (rid, p), v in got.items():
         assert np.isfinite(v).all(), f"non-finite logits at {rid}:{p}"
-        d = np.abs(v.astype(np.float64) - ref[rid][p])
-        limit = tol_max * scale
-        if slack is not None and 4 * slack[rid][p] > limit:
-            limit = 4 * slack[rid][p]
-        else:
+    if dtype == torch.float32:
+        scale = max(np.abs(r).max() for r in ref.values())
+        means = []
+        for (rid, p), v in sorted(got.items()):
+            d = np.abs(v.astype(np.float64) - ref[rid][p])
             means.append(d.mean())
-        assert d.max() <= limit, f"first wrong position: request {rid} position {p}: |diff| {d.max():.3g} > {limit:.3g}"
-    if slack is not None:
-        assert np.median([4 * s for v in slack.values() for s in v]) <= 6 * tol_max * scale
-    if means:
-        assert np.mean(means) <= 2 * tol_mean * scale
+            assert d.max() <= TOL32[0] * scale, f"first wrong position: request {rid} position {p}: |diff| {d.max():.3g}"
+        assert np.mean(means) <= TOL32[1] * scale
+        return
+    scale = np.sqrt(np.mean(np.concatenate([centred_rms(r) ** 2 for r in ref.values()])))
+    ratios, over = [], []
+    for (rid, p), v in sorted(got.items()):
+        e = centred_rms(v.astype(np.float64) - ref[rid][p]) / scale
+        s = slack[rid][p] / scale + FLOOR
+        assert e <= SINGLE * s, f"first wrong position: request {rid} position {p}: error {e:.3g}, rounding alone {s:.3g}"
+        ratios.append(e / s)
+        if e > OVER * s:
+            over.append((rid, p))
+    assert len(over) <= max(1, OVER_SHARE * len(ratios)), f"{len(over)} of {len(ratios)} positions are beyond rounding, the first {over[0]}"
+    assert np.median(ratios) <= MEDIAN, f"the median error is {np.median(ratios):.2f} times what rounding alone does"
 
 
 def check(got, cfg, weights, seqs, ref, dtype):
@@ -113,7 +128,6 @@ def test_captured_decode_steps_equal_eager_ones(tmp_path_factory, which, dtype):
         runs.append(helpers.run_trace_on_engine(engine, steps))
         if graphs:
             assert any(g.graph is not None for g in engine._graphs.values())
-    scale = max(np.abs(v).max() for v in runs[1].values())
     for key, v in runs[0].items():
         if dtype == torch.float32:
             assert np.array_equal(v, runs[1][key]), key
