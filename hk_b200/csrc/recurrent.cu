@@ -492,8 +492,11 @@ HK_API int hk_mingru_scan(const float* proj, long long ld, const float* z_bias, 
 // of a segment's tokens; the threads of the first chunk read the old tail before they write the new one, and
 // nobody else touches it.
 #define SC_TOKENS 32
+#define SC_GROUP 8
 #define SC_MAX_TAPS 16
 
+// The thread walks its tokens in groups of SC_GROUP: the group's inputs are loaded at once (each input is read once; the
+// taps - 1 before them stay in registers from the group before), then the group's outputs are summed, oldest tap first.
 __global__ void __launch_bounds__(128)
 short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w, const int* __restrict__ segs,
                   float* __restrict__ tail, float* __restrict__ y, long long ldy, int C, int taps) {
@@ -504,19 +507,39 @@ short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __res
   if (c >= C || t0 >= count) return;
   const int back = taps - 1;
   float* tl = tail + (size_t)slot * back * C + c;
-  float wc[SC_MAX_TAPS];
-#pragma unroll
-  for (int j = 0; j < SC_MAX_TAPS; ++j) wc[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
   auto input = [&](int r) -> float {            // the request's input r rows from the segment's first (r may be negative)
     return r >= 0 ? x[(size_t)(row0 + r) * ldx + c] : tl[(size_t)(back + r) * C];
   };
-  const int t1 = min(count, t0 + SC_TOKENS);
-  for (int t = t0; t < t1; ++t) {
-    float acc = 0.f;
+  float wr[SC_MAX_TAPS];                        // wr[s]: the weight of the input s tokens back
+  float hist[SC_MAX_TAPS];                      // hist[s], s >= 1: the input s tokens before the group's first
 #pragma unroll
-    for (int j = 0; j < SC_MAX_TAPS; ++j)
-      if (j < taps) acc = fmaf(wc[j], input(t - back + j), acc);
-    y[(size_t)(row0 + t) * ldy + c] = acc / (1.0f + expf(-acc));
+  for (int s = 0; s < SC_MAX_TAPS; ++s) {
+    wr[s] = s <= back ? w[(size_t)c * taps + back - s] : 0.f;
+    hist[s] = (s >= 1 && s <= back) ? input(t0 - s) : 0.f;
+  }
+  const int t1 = min(count, t0 + SC_TOKENS);
+  for (int tg = t0; tg < t1; tg += SC_GROUP) {
+    float nw[SC_GROUP];
+#pragma unroll
+    for (int u = 0; u < SC_GROUP; ++u) nw[u] = tg + u < t1 ? x[(size_t)(row0 + tg + u) * ldx + c] : 0.f;
+    float acc[SC_GROUP];
+#pragma unroll
+    for (int u = 0; u < SC_GROUP; ++u) acc[u] = 0.f;
+#pragma unroll
+    for (int s = SC_MAX_TAPS - 1; s >= 0; --s) {
+      if (s <= back) {
+#pragma unroll
+        for (int u = 0; u < SC_GROUP; ++u) acc[u] = fmaf(wr[s], u >= s ? nw[u - s] : hist[s - u], acc[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < SC_GROUP; ++u)
+      if (tg + u < t1) y[(size_t)(row0 + tg + u) * ldy + c] = acc[u] / (1.0f + expf(-acc[u]));
+    float next[SC_MAX_TAPS];
+#pragma unroll
+    for (int s = 1; s < SC_MAX_TAPS; ++s) next[s] = s <= SC_GROUP ? nw[SC_GROUP - s] : hist[s - SC_GROUP];
+#pragma unroll
+    for (int s = 1; s < SC_MAX_TAPS; ++s) hist[s] = next[s];
   }
   if (blockIdx.z == 0 && back > 0) {
     float keep[SC_MAX_TAPS];
@@ -613,33 +636,61 @@ HK_API int hk_gated_delta_scan(const float* q, const float* k, const float* v, l
 // gate i = cap tanh((il + bi) / cap) and the log forget gate f = logsigmoid(cap tanh((fl + bf) / cap)):
 //     m_t = max(f + m_(t-1), i);  S_t = e^(f + m_(t-1) - m_t) S_(t-1) + e^(i - m_t) k v^T;  n_t likewise with k alone
 //     o = S_t^T q / (max(|n_t . q|, e^(-m_t)) + den_eps)
-// The maxima are a scalar recurrence per (request, head): one thread walks it and leaves, per token, the three
+// The maxima are a scalar recurrence per (request, head): one warp walks it and leaves, per token, the three
 // exponentials.  n rides along as one more column of S whose value is always 1 (the state is [dk, dvp] with
 // dvp = dv + 1 rounded up to 4; the columns past dv + 1 stay zero), so the delta rule's scan runs the matrix part
 // with the record (d, a*u, u, k, r, v) = (keep, 0, 0, take k, q, [v | 1 | 0..]) and hands back S^T q and n . q together.
 __device__ __forceinline__ float logsigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-__global__ void mlstm_gates_kernel(const float* __restrict__ il, const float* __restrict__ fl, long long ld,
-                                   const float* __restrict__ i_bias, const float* __restrict__ f_bias, const int* __restrict__ segs,
-                                   float* __restrict__ m_state, float* __restrict__ gates, int n_seg, int H, float cap) {
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+// A warp per (request, head) walks the maxima: 32 tokens at a time every lane turns its token's logits into the two
+// log gates (the next 32 tokens' logits already on their way), then the chain m' = max(f + m, i) runs down the 32
+// tokens in order, in every lane alike, and every lane writes its token's three exponentials.
+__global__ void __launch_bounds__(128)
+mlstm_gates_kernel(const float* __restrict__ il, const float* __restrict__ fl, long long ld, const float* __restrict__ i_bias,
+                   const float* __restrict__ f_bias, const int* __restrict__ segs, float* __restrict__ m_state,
+                   float* __restrict__ gates, int n_seg, int H, float cap) {
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
   if (idx >= n_seg * H) return;
   const int seg = idx / H, h = idx % H;
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
   const float bi = i_bias[h], bf = f_bias[h];
   float m = m_state[(size_t)slot * H + h];
-  for (int t = 0; t < count; ++t) {
-    const size_t row = (size_t)(row0 + t);
-    const float ig = cap * tanhf((il[row * ld + h] + bi) / cap);
-    const float fg = logsigmoid_f(cap * tanhf((fl[row * ld + h] + bf) / cap));
-    const float mn = fmaxf(fg + m, ig);
-    float* o = gates + (row * H + h) * 3;
-    o[0] = expf(fg + m - mn);
-    o[1] = expf(ig - mn);
-    o[2] = expf(-mn);
-    m = mn;
+  float xi = 0.f, xf = 0.f;
+  if (lane < count) {
+    xi = il[(size_t)(row0 + lane) * ld + h];
+    xf = fl[(size_t)(row0 + lane) * ld + h];
   }
-  m_state[(size_t)slot * H + h] = m;
+  for (int t0 = 0; t0 < count; t0 += 32) {
+    const int tc = min(32, count - t0);
+    float ni = 0.f, nf = 0.f;
+    if (t0 + 32 + lane < count) {
+      ni = il[(size_t)(row0 + t0 + 32 + lane) * ld + h];
+      nf = fl[(size_t)(row0 + t0 + 32 + lane) * ld + h];
+    }
+    const float ig = cap * tanhf((xi + bi) / cap);
+    const float fg = logsigmoid_f(cap * tanhf((xf + bf) / cap));
+    float before = 0.f, after = 0.f;
+#pragma unroll 8
+    for (int j = 0; j < tc; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, fg, j), ij = __shfl_sync(0xffffffffu, ig, j);
+      const float mn = fmaxf(fj + m, ij);
+      if (lane == j) {
+        before = m;
+        after = mn;
+      }
+      m = mn;
+    }
+    if (lane < tc) {
+      float* o = gates + ((size_t)(row0 + t0 + lane) * H + h) * 3;
+      o[0] = expf(fg + before - after);
+      o[1] = expf(ig - after);
+      o[2] = expf(-after);
+    }
+    xi = ni;
+    xf = nf;
+  }
+  if (lane == 0) m_state[(size_t)slot * H + h] = m;
 }
 
 __global__ void mlstm_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
@@ -682,7 +733,7 @@ HK_API int hk_mlstm_scan(const float* q, const float* k, const float* v, const f
   const int dvp = hk_mlstm_padded(dv);
   int L, rpt;
   if (!dr_plan(n_seg, H, dk, dvp, &L, &rpt)) return HK_ERR_UNSUPPORTED;
-  int e = hk_launch(mlstm_gates_kernel, dim3((unsigned)((n_seg * H + 63) / 64)), dim3(64), 0, s, il, fl, ld, i_bias, f_bias, segs,
+  int e = hk_launch(mlstm_gates_kernel, dim3((unsigned)((n_seg * H + 3) / 4)), dim3(128), 0, s, il, fl, ld, i_bias, f_bias, segs,
                     m_state, gates, n_seg, H, cap);
   if (e) return e;
   const long long items = (long long)n_rows * H;

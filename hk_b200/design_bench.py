@@ -116,10 +116,18 @@ def model_points(raw: dict, prompt: int, batches, steps: int, warmup: int, reps:
     return out
 
 
-def _time_kernel(fn, reps: int = 7):
-    """Median device time in microseconds of `fn()`, L2 flushed before every timed call."""
+def _time_kernel(fn, reps: int = 7, replay: bool = False):
+    """Median device time in microseconds of `fn()`, L2 flushed before every timed call.  `replay`: the call is captured
+    in a CUDA graph once and the graph's replay is timed, as decode steps run: the host's part of the call is left out."""
     import torch
     flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+    if replay:
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        fn = graph.replay
     times = []
     for i in range(reps + 3):
         flush.fill_(float(i))
@@ -406,19 +414,192 @@ def padodra_kernel_points(width: int, n: int, context: int, peaks: dict) -> dict
     return out
 
 
+def mifolorn_shape(width: int, passes: int = 2, vocab: int = 32000) -> dict:
+    """Layer sizes that resemble a real model's: an attention with heads of 128, four query heads per key head, half of
+    every head rotated with scaled frequencies, a soft cap and an output gate, beside a gated delta rule with heads of 64
+    (two value heads per query/key head, four taps); a matrix memory and a gated delta rule with as many heads of 64 as
+    the width holds; feed-forwards of three times the width; a token input of 64 per layer; the four layers run
+    `passes` times."""
+    heads128, heads64 = width // 128, width // 64
+    rot = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    left = {"dim": 128, "heads": heads128, "kv_heads": max(1, heads128 // 4), "vdim": 128, "scale": 1.0 / math.sqrt(128.0),
+            "softcap": 50.0, "rot": rot}
+    right = {"dim": 64, "heads": heads128, "kv_heads": max(1, heads128 // 2), "vdim": 64, "conv": 4}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}}
+    mem = {"type": "mlstm", "mixer": {"dim": 64, "heads": heads64, "vdim": 64, "gate_cap": 15.0}}
+    dlt = {"type": "delta", "mixer": {"dim": 64, "heads": heads64, "kv_heads": max(1, heads64 // 2), "vdim": 64, "conv": 4}}
+    dense = {"kind": "dense", "ff": 3 * width}
+    layers = [dict(par, mlp=dense), dict(par, mlp=dense), dict(mem, mlp=dense), dict(dlt, mlp=dense)]
+    return {"architecture": "Mifolorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "token_side": {"dim": 64}, "loop": {"start": 0, "stop": len(layers), "times": passes}, "layers": layers,
+            "initializer_range": 0.02}
+
+
+def mifolorn_kernel_points(width: int, n: int, decode: bool, peaks: dict) -> dict:
+    """The design's kernels alone at a layer of this width, each beside the like kernel of the Kedanex decoder: one
+    request of n prompt tokens, or (decode) n requests that each bring one token (the attention over 2,047 cached ones;
+    these are timed as replays of a captured graph)."""
+    import numpy as np
+    import torch
+
+    from .csrc import attention_fast, ops
+    dev = "cuda"
+    bw, tc = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    out = {}
+
+    def note(name, us, nbytes, flops, peak_flops, like=None):
+        floor = max(nbytes / bw, flops / peak_flops if peak_flops else 0.0) * 1e6
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "flops": int(flops), "roofline_us": round(floor, 2),
+                     "of_roofline": round(floor / us, 3), **({"like": like} if like else {})}
+
+    count, rows = (n, 1) if decode else (1, n)
+    _time_kernel = lambda fn: globals()["_time_kernel"](fn, replay=decode)      # decode steps replay a captured graph
+    sg = torch.tensor([[i, i * rows, rows] for i in range(count)], dtype=torch.int32, device=dev)
+    H, G, dk, dv, taps = width // 64, width // 128, 64, 64, 4
+    K, V = G * dk, H * dv
+    C = 2 * K + V
+    fp32 = FP32_TFLOPS * 1e12
+
+    # ---- gated delta rule: the short convolution, the scan (its preparation and the walk), the output's norm and gate
+    proj = torch.randn(n, C + V + 2 * H, device=dev) * 0.5
+    act = torch.empty(n, C, device=dev)
+    conv = torch.randn(C, taps, device=dev) * 0.3
+    tail = torch.zeros(count, taps - 1, C, device=dev)
+    us = _time_kernel(lambda: ops.short_conv(proj[:, :C], conv, sg, tail, act))
+    note("short_conv (q, k and v of a gated delta rule)", us, n * C * 8 + count * (taps - 1) * C * 8, 2.0 * n * C * taps, fp32,
+         like="rms_norm_add (row-wise)")
+    state = torch.zeros(count, H, dk, dv, device=dev)
+    o = torch.empty(n, V, device=dev)
+    a_log, dt_bias = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+    us = _time_kernel(lambda: ops.gated_delta_scan(act[:, :K], act[:, K:2 * K], act[:, 2 * K:], proj[:, C + V:C + V + H], proj[:, C + V + H:],
+                                                   a_log, dt_bias, sg, state, o, H, G, dk, dv, dk ** -0.5, 1e-6))
+    note("gated_delta_scan", us, 4 * (n * (2 * K + 2 * V + 2 * H) + 2 * count * H * dk * dv), 8.0 * n * H * dk * dv, fp32,
+         like="delta_rule_scan (Kedanex)")
+    # the like kernel: the generalised delta rule at the same heads (its decays and removal strengths are vectors per head)
+    KK = H * dk
+    projk = torch.randn(n, 4 * KK, device=dev) * 0.5
+    wl = torch.randn(n, KK, device=dev)
+    zb = torch.zeros(KK, device=dev)
+    ok = torch.empty(n, KK, device=dev)
+    us = _time_kernel(lambda: ops.delta_rule_scan(projk[:, :KK], projk[:, KK:2 * KK], projk[:, 2 * KK:3 * KK], projk[:, 3 * KK:], wl, zb, zb, sg,
+                                                  state, ok, H, dk, dk, math.exp(-0.5), 1e-6))
+    note("delta_rule_scan (Kedanex)", us, 4 * (6 * n * KK + 2 * count * H * dk * dk), 8.0 * n * H * dk * dk, fp32)
+    og = torch.empty(n, V, dtype=torch.bfloat16, device=dev)
+    wn = torch.ones(dv, device=dev)
+    us = _time_kernel(lambda: ops.head_out_gate(o, proj[:, C:C + V], wn, 1e-5, og, H, dv, act="silu"))
+    note("head_out_gate (delta rule: shared weight, silu)", us, n * V * (4 + 4 + 2), 0, 0, like="head_norm_gate (Kedanex)")
+    wk = torch.ones(V, device=dev)
+    us = _time_kernel(lambda: ops.head_norm_gate(o, proj[:, C:C + V], wk, 1e-5, og, H, dv))
+    note("head_norm_gate (Kedanex)", us, n * V * (4 + 4 + 2), 0, 0)
+
+    # ---- matrix memory: the gates' walk, the preparation and the scan; its output's normaliser, norm and gate
+    dvp = ops.mlstm_padded(dv)
+    projm = torch.randn(n, 2 * KK + 2 * V + 2 * H, device=dev) * 0.5
+    st_m = torch.zeros(count, H, dk, dvp, device=dev)
+    m_st = torch.zeros(count, H, device=dev)
+    om = torch.empty(n, H * dvp, device=dev)
+    gates = torch.empty(n, H, 3, device=dev)
+    ib = torch.zeros(H, device=dev)
+
+    def memory():
+        st_m.zero_()
+        m_st.zero_()
+        ops.mlstm_scan(projm[:, :KK], projm[:, KK:2 * KK], projm[:, 2 * KK:2 * KK + V], projm[:, 2 * KK + 2 * V:2 * KK + 2 * V + H],
+                       projm[:, 2 * KK + 2 * V + H:], ib, ib, sg, st_m, m_st, om, gates, H, dk, dv, 15.0, dk ** -0.5)
+
+    us = _time_kernel(memory)
+    note("mlstm_scan", us, 4 * (n * (2 * KK + 2 * V + 2 * H) + 2 * count * H * dk * dvp), 5.0 * n * H * dk * (dv + 1), fp32,
+         like="delta_rule_scan (Kedanex)")
+    us = _time_kernel(lambda: ops.head_out_gate(om, projm[:, 2 * KK + V:2 * KK + 2 * V], wk, 1e-5, og, H, dv, act="sigmoid", gates=gates,
+                                                den_eps=1e-6))
+    note("head_out_gate (matrix memory: normaliser, sigmoid)", us, n * V * (4 + 4 + 2), 0, 0, like="head_norm_gate (Kedanex)")
+
+    # ---- attention: heads of 128 with a soft cap and the output gate; and Kedanex's, with its window and sink
+    Ha, Ga, hd, pt, context = width // 128, max(1, width // 512), 128, 64, 2047
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    per = (context + 1) if decode else n
+    ppr = -(-per // pt)
+    table = torch.arange(count * ppr, dtype=torch.int32, device=dev).view(count, ppr).contiguous()
+    slots = list(range(count))
+    q_starts = list(range(n)) if decode else [0]
+    q_lens = [1] * n if decode else [n]
+    starts = [context] * n if decode else [0]
+    positions = torch.tensor([context] * n if decode else list(range(n)), dtype=torch.int32, device=dev)
+    slot_of = torch.tensor(list(range(n)) if decode else [0] * n, dtype=torch.int32, device=dev)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    pairs = n * (context + 1) if decode else n * (n + 1) // 2
+    kp = (torch.randn(count * ppr, Ga, pt, hd, device=dev) * 0.5).bfloat16()
+    vp = (torch.randn(count * ppr, Ga, pt, hd, device=dev) * 0.5).bfloat16()
+    q = (torch.randn(n, Ha * hd, device=dev) * 0.5).bfloat16()
+    att = torch.empty(n, Ha * hd, dtype=torch.bfloat16, device=dev)
+    gate = torch.randn(n, Ha * hd, device=dev)
+    fixed = attention_fast.decode_splits(n, Ga, sm) if decode else 0
+    rws = 256 if (not decode and attention_fast.tc2_prefill_supported(hd, Ha // Ga, pt)) else (128 if not decode else 64)
+    plan = attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, Ha, Ga, sm, up, fixed_splits=fixed,
+                                     max_context=context + 64 if decode else 0, prefill_rows=rws)
+    keys = (n * (context + 1) if decode else n) * Ga * hd * 4
+    us = _time_kernel(lambda: ops.paged_attention(q, kp, vp, table, positions, slot_of, att, Ha, Ga, hd, pt, 0, hd ** -0.5, plan=plan,
+                                                  softcap=50.0, gate=gate, gate_scale=0.8))
+    note("attention with soft cap and output gate", us, keys + n * Ha * hd * (4 + 4 + 4), 4.0 * pairs * Ha * hd, tc,
+         like="attention with a sink (Kedanex; no window here)")
+    us = _time_kernel(lambda: ops.paged_attention(q, kp, vp, table, positions, slot_of, att, Ha, Ga, hd, pt, 0, hd ** -0.5, plan=plan,
+                                                  sink=True))
+    note("attention with a sink (Kedanex; no window here)", us, keys + n * Ha * hd * 4, 4.0 * pairs * Ha * hd, tc)
+    qkv = torch.randn(n, (Ha + 2 * Ga) * hd, device=dev)
+    bias = torch.zeros((Ha + 2 * Ga) * hd, device=dev)
+    qn = torch.ones(hd, device=dev)
+    cos = torch.ones(per + 1, 32, device=dev)
+    sin = torch.zeros(per + 1, 32, device=dev)
+    us = _time_kernel(lambda: ops.qk_norm_rope_kv_write(qkv, q, qn, qn, 1e-5, cos, sin, 64, positions, slot_of, table, kp, vp, Ha, Ga, hd, pt,
+                                                        bias=bias))
+    note("qk_norm_rope_kv_write with biases and half-rotated heads", us, n * (Ha + 2 * Ga) * hd * 6, 0, 0,
+         like="qk_norm_rope_kv_write (whole heads rotated, no bias)")
+    cos2 = torch.ones(per + 1, hd // 2, device=dev)
+    sin2 = torch.zeros(per + 1, hd // 2, device=dev)
+    us = _time_kernel(lambda: ops.qk_norm_rope_kv_write(qkv, q, qn, qn, 1e-5, cos2, sin2, hd, positions, slot_of, table, kp, vp, Ha, Ga, hd, pt))
+    note("qk_norm_rope_kv_write (whole heads rotated, no bias)", us, n * (Ha + 2 * Ga) * hd * 6, 0, 0)
+
+    # ---- the per-layer token input and the layer's row-wise kernels
+    side = 64
+    x = torch.randn(n, width, device=dev)
+    xb = torch.empty(n, width, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.narrow(x, xb))
+    note("narrow (the token input reads the stream itself)", us, n * width * 6, 0, 0, like="rms_norm")
+    z = torch.randn(n, side, device=dev)
+    tab = (torch.randn(32000, 4 * side, device=dev) * 0.1).bfloat16()
+    ids = torch.randint(0, 32000, (n,), dtype=torch.int32, device=dev)
+    g = torch.empty(n, side, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.token_gate(z, tab, side, ids, g))
+    note("token_gate", us, n * side * (4 + 2 + 2), 0, 0, like="swiglu (row-wise)")
+    res = torch.randn(n, width, device=dev)
+    wnn = torch.ones(width, device=dev)
+    us = _time_kernel(lambda: ops.rms_norm_add(x, wnn, 1e-5, res))
+    note("rms_norm_add (row-wise)", us, n * width * 12, 0, 0)
+    us = _time_kernel(lambda: ops.rms_norm(x, wnn, 1e-5, xb))
+    note("rms_norm", us, n * width * 6, 0, 0)
+    gu = torch.randn(n, 2 * side, device=dev)
+    us = _time_kernel(lambda: ops.swiglu(gu, g))
+    note("swiglu (row-wise)", us, n * side * 10, 0, 0)
+    return out
+
+
 def run(design: str, args, peaks: dict) -> dict:
-    if design not in ("kedanex", "padodra"):
-        raise SystemExit(f"bench.py --design: unknown design '{design}' (known: kedanex, padodra)")
+    if design not in ("kedanex", "padodra", "mifolorn"):
+        raise SystemExit(f"bench.py --design: unknown design '{design}' (known: kedanex, padodra, mifolorn)")
     widths = [int(w) for w in str(args.design_widths).split(",")]
     sizes = {}
     for width in widths:
         t0 = time.time()
-        ours = kedanex_shape(width) if design == "kedanex" else padodra_shape(width)
-        theirs = qwen3_shape(width, len(ours["layers"]))
+        ours = {"kedanex": kedanex_shape, "padodra": padodra_shape, "mifolorn": mifolorn_shape}[design](width)
+        runs = len(ours["layers"]) * (ours["loop"]["times"] if "loop" in ours else 1)
+        beside, theirs = ("kedanex", kedanex_shape(width, runs // 4)) if design == "mifolorn" else ("qwen3", qwen3_shape(width, runs))
         entry = {design: model_points(ours, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
-                 "qwen3": model_points(theirs, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
-                 "layer_runs": len(ours["layers"])}
-        if design == "kedanex":
+                 beside: model_points(theirs, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
+                 "layer_runs": runs}
+        if design == "mifolorn":
+            entry["kernels_prefill_2048_rows"] = mifolorn_kernel_points(width, 2048, False, peaks)
+            entry["kernels_decode_64_rows"] = mifolorn_kernel_points(width, 64, True, peaks)
+        elif design == "kedanex":
             entry["kernels_prefill_2048_rows"] = kernel_points(width, 2048, peaks)
             entry["kernels_decode_64_rows"] = {k: v for k, v in kernel_points(width, 64, peaks).items() if "request" not in k or "decode" in k}
         else:
@@ -428,7 +609,7 @@ def run(design: str, args, peaks: dict) -> dict:
         sizes[f"width{width}"] = entry
         print(f"[bench] design {design}, width {width}: {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
     k = sizes[f"width{widths[-1]}"]
-    return {"metric": f"{design} prefill and decode tok/s beside Qwen3 at equal width and depth", "value": k[design]["decode_b8"]["tok_s"],
+    return {"metric": f"{design} prefill and decode tok/s beside {'Kedanex' if design == 'mifolorn' else 'Qwen3'} at equal width and depth", "value": k[design]["decode_b8"]["tok_s"],
             "unit": "tokens/s (decode, batch 8, largest width)", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "higher_is_better": True, "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
             "impl": "ours", "design": design, "sizes": sizes, "peaks": peaks}

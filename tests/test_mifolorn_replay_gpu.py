@@ -128,11 +128,15 @@ def test_captured_decode_steps_equal_eager_ones(tmp_path_factory, which, dtype):
         runs.append(helpers.run_trace_on_engine(engine, steps))
         if graphs:
             assert any(g.graph is not None for g in engine._graphs.values())
-    for key, v in runs[0].items():
-        if dtype == torch.float32:
+    if dtype == torch.float32:
+        for key, v in runs[0].items():
             assert np.array_equal(v, runs[1][key]), key
-        else:       # a captured step cuts a request's keys into a fixed number of ranges, an eager one by the batch: other sums
-            assert np.abs(v - runs[1][key]).max() <= 2e-2 * scale, key
+    else:
+        # a captured step cuts a request's keys into a fixed number of ranges, an eager one by the batch: other sums, and
+        # so other roundings downstream; the two runs differ as either differs from the plain logits
+        _, cfg, weights, seqs, ref = setup_case(tmp_path_factory, which, dtype)
+        eager = {rid: np.stack([runs[1][(rid, p)] for p in range(len(ids))]).astype(np.float64) for rid, ids in seqs.items()}
+        compare(runs[0], eager, seqs, dtype, rounding_alone(cfg, weights, seqs, ref))
 
 
 @pytest.mark.parametrize("which", ["U", "W"])
