@@ -205,13 +205,23 @@ def tma_decode_supported(hd: int, group: int, page_tokens: int) -> bool:
     return hd in (64, 128) and group <= 16 and page_tokens >= 16 and page_tokens & (page_tokens - 1) == 0
 
 
+GATED = 2       # what `run` returns when the kernel it took also applied the output gate
+
+
 def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan: FlashPlan,
-        allow_tma: bool = True, sink: bool = False, sinks=None, softcap: float = 0.0, chunk: int = 0) -> bool:
+        allow_tma: bool = True, sink: bool = False, sinks=None, softcap: float = 0.0, chunk: int = 0, gate=None,
+        gate_scale: float = 1.0):
+    """Runs the step on the flash kernels.  Returns False when they refuse it, True when `out` holds the attention, and
+    GATED when it holds the attention times gate_scale * sigmoid(gate) (the tcgen05 prompt kernels apply a gate whose
+    rows are 16-byte aligned in their epilogue; after any other kernel the caller applies it)."""
     from . import gemm_fast, ops
     if not supported(hd, H // G) or plan is None:
         return False
     sk = 1 if sink else 0
     extra = (_ptr(sinks), ctypes.c_float(softcap), int(chunk))
+    fused_gate = gate is not None and gate.data_ptr() % 16 == 0 and gate.stride(0) % 4 == 0 and gate.stride(1) == 1
+    gate_args = (_ptr(gate if fused_gate else None), ctypes.c_longlong(gate.stride(0) if fused_gate else 0), ctypes.c_float(gate_scale))
+    done = GATED if fused_gate else True
     lib = build.load("attention_flash")
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     rows = 16 * plan.nw
@@ -227,11 +237,11 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
             _ptr(q), _ptr(k_pages), _ptr(v_pages), ctypes.c_longlong(k_pages.shape[0]), _ptr(block_table),
             int(block_table.shape[1]), _ptr(plan.items), plan.n_items, _ptr(out), H, G, hd, int(page_tokens), int(window),
             ctypes.c_float(scale * math.log2(math.e)), plan.max_keys // int(page_tokens) + 2,
-            _ptr(gemm_fast.status_flag(q.device)), sk, *extra, stream)
+            _ptr(gemm_fast.status_flag(q.device)), sk, *extra, *gate_args, stream)
         if code == _UNSUPPORTED:
             return False
         ops._check(code, "paged_attention (tcgen05 prefill, two query tiles)")
-        return True
+        return done
     if plan.nw == 8:
         if plan.n_parts or not tc_prefill_supported(hd, H // G):
             return False
@@ -239,11 +249,11 @@ def run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, sc
         code = lib_tc.hk_attention_prefill_tc(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), int(block_table.shape[1]), _ptr(plan.items),
             plan.n_items, _ptr(out), H, G, hd, int(page_tokens), int(window), ctypes.c_float(scale * math.log2(math.e)),
-            plan.max_keys // int(page_tokens) + 2, _ptr(gemm_fast.status_flag(q.device)), sk, *extra, stream)
+            plan.max_keys // int(page_tokens) + 2, _ptr(gemm_fast.status_flag(q.device)), sk, *extra, *gate_args, stream)
         if code == _UNSUPPORTED:
             return False
         ops._check(code, "paged_attention (tcgen05 prefill)")
-        return True
+        return done
     code = _UNSUPPORTED
     if plan.nw == 1 and allow_tma and tma_decode_supported(hd, H // G, int(page_tokens)):
         code = lib.hk_attention_decode_tma(

@@ -51,16 +51,43 @@ struct ScoreOpts {
   int sink;             // 1: one more term in the softmax's denominator, a key without a value
   const float* sinks;   // its score per query head (natural units); null: 0
   float cap_log2;       // soft cap c on the scores, times log2(e): s <- c tanh(s / c); 0: none
-  float cap_in;         // scale / c
+  float cap_in2;        // 2 log2(e) scale / c: a raw dot product times this is 2 z log2(e), z = score / c
   int chunk;            // a row at position p sees no key before (p / chunk) * chunk; 0: no such mask
+  const float* gate;    // output gate's logits, float32 [tokens, gate_ld >= H * HD] (16-byte aligned rows), or null:
+  long long gate_ld;    //   out[t, h, d] is multiplied by gate_scale * sigmoid(gate[t, h * HD + d]) before it is rounded
+  float gate_scale;
 };
 
-// a raw dot product (or -inf for a masked key) into the capped score in the base-2 exponent domain
+// eight values of a row of O, normalised and (with a gate) gated, packed into bfloat16
+__device__ __forceinline__ uint4 finish8(const uint32_t* o, float inv, const float* gp, float gate_scale) {
+  float f[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[e]) * inv;
+  if (gp != nullptr) {
+    const float4 a = *reinterpret_cast<const float4*>(gp), b = *reinterpret_cast<const float4*>(gp + 4);
+    const float gl[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = __fdividef(f[e] * gate_scale, 1.0f + __expf(-gl[e]));   // the result is rounded to bfloat16
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    __nv_bfloat162 pk = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+    w[e] = *reinterpret_cast<uint32_t*>(&pk);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// a raw dot product (or -inf for a masked key) into the capped score in the base-2 exponent domain:
+// c log2(e) tanh(z) = C - 2 C / (e^(2z) + 1) with z = score / c and C = c log2(e).  The softmax threads are bound by the
+// instructions they issue, so the exponential and the reciprocal are the bare special-function instructions (both
+// saturate the right way: e^(2z) = inf gives C, 0 gives -C) and the rest is one multiplication, one addition and one
+// fused multiply-add.  Absolute error of the tanh about 2e-7.
 __device__ __forceinline__ uint32_t capped_score(uint32_t raw, const ScoreOpts& so) {
-  const float x = __uint_as_float(raw);
-  const float t = exp2f(2.8853900817779268f * x * so.cap_in);        // e^(2 x scale / c)
-  const float y = so.cap_log2 * (1.0f - __fdividef(2.0f, t + 1.0f));  // c log2(e) tanh(x scale / c)
-  return raw == 0xff800000u ? raw : __float_as_uint(y);
+  float t, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(__uint_as_float(raw) * so.cap_in2));      // e^(2 z)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t + 1.0f));
+  return raw == 0xff800000u ? raw : __float_as_uint(fmaf(-2.0f * so.cap_log2, r, so.cap_log2));
 }
 
 
@@ -481,7 +508,9 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     if (ok && last >= 0 && __all_sync(0xffffffffu, mbar_wait(&sm.pv_done[last & 1], (uint32_t)((last >> 1) & 1), abort_flag))) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
-      bf16* op = out + ((size_t)(it.q_row0 + (valid ? tq : 0)) * H + g * group + (valid ? r % group : 0)) * HD + half * HO;
+      const int out_row = it.q_row0 + (valid ? tq : 0), out_head = g * group + (valid ? r % group : 0);
+      bf16* op = out + ((size_t)out_row * H + out_head) * HD + half * HO;
+      const float* gp = so.gate ? so.gate + (size_t)out_row * so.gate_ld + (size_t)out_head * HD + half * HO : nullptr;
 #pragma unroll
       for (int c0 = 0; c0 < HO; c0 += 32) {
         uint32_t o[32];
@@ -489,15 +518,8 @@ attention_prefill_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__
         tmem_ld_wait();
         if (valid) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * e]) * inv, __uint_as_float(o[i + 2 * e + 1]) * inv);
-              w[e] = *reinterpret_cast<uint32_t*>(&pk);
-            }
-            *reinterpret_cast<uint4*>(op + c0 + i) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(op + c0 + i) = finish8(o + i, inv, gp ? gp + c0 + i : nullptr, so.gate_scale);
         }
       }
     }
@@ -844,7 +866,9 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
         float l = l0 + l1;
         if (so.sink && valid) l += exp2f((so.sinks ? so.sinks[g * group + row % group] * 1.4426950408889634f : 0.f) - m);
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        bf16* op = out + ((size_t)(it.q_row0 + (valid ? tq : 0)) * H + g * group + (valid ? row % group : 0)) * HD;
+        const int out_row = it.q_row0 + (valid ? tq : 0), out_head = g * group + (valid ? row % group : 0);
+        bf16* op = out + ((size_t)out_row * H + out_head) * HD;
+        const float* gp = so.gate ? so.gate + (size_t)out_row * so.gate_ld + (size_t)out_head * HD : nullptr;
         // the whole row of O at once (the registers that held scores are free now): one wait instead of HD / 32
         uint32_t o[HD];
 #pragma unroll
@@ -852,15 +876,8 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __
         tmem_ld_wait();
         if (valid) {
 #pragma unroll
-          for (int i = 0; i < HD; i += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * e]) * inv, __uint_as_float(o[i + 2 * e + 1]) * inv);
-              w[e] = *reinterpret_cast<uint32_t*>(&pk);
-            }
-            *reinterpret_cast<uint4*>(op + i) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          for (int i = 0; i < HD; i += 8)
+            *reinterpret_cast<uint4*>(op + i) = finish8(o + i, inv, gp ? gp + i : nullptr, so.gate_scale);
         }
       }
     }
@@ -918,11 +935,12 @@ int launch2(const CUtensorMap& mk, const CUtensorMap& mv, const void* q, const i
                    (bf16*)out, H, G, pt, window, scale_log2, so, pages_cap, status);
 }
 
-ScoreOpts make_opts(int sink, const float* sinks, float softcap, float scale_log2, int chunk) {
-  ScoreOpts so = {sink, sink ? sinks : nullptr, 0.f, 0.f, chunk > 0 ? chunk : 0};
+ScoreOpts make_opts(int sink, const float* sinks, float softcap, float scale_log2, int chunk, const float* gate, long long gate_ld,
+                    float gate_scale) {
+  ScoreOpts so = {sink, sink ? sinks : nullptr, 0.f, 0.f, chunk > 0 ? chunk : 0, gate, gate_ld, gate_scale};
   if (softcap > 0.f) {
     so.cap_log2 = softcap * 1.4426950408889634f;
-    so.cap_in = scale_log2 / so.cap_log2;       // scale / softcap
+    so.cap_in2 = 2.8853900817779268f * scale_log2 / so.cap_log2;       // 2 log2(e) scale / softcap
   }
   return so;
 }
@@ -933,13 +951,16 @@ ScoreOpts make_opts(int sink, const float* sinks, float softcap, float scale_log
 // of the first token, first key, one past the last key, -1, 0}.  pages_cap: the most pages an item's key range spans.  Writes out[token, head, :] directly (no key
 // splitting).  `status` is a device int set to 3 if a wait timed out.  Refuses (HK_ERR_UNSUPPORTED) head sizes
 // other than 64 and 128 and groups above 128 heads.  sink, sinks, softcap, chunk: see `ScoreOpts` (sinks: one score per
-// query head or null; softcap and chunk 0 for none).
+// query head or null; softcap and chunk 0 for none).  gate (float32 logits [tokens, gate_ld], 16-byte aligned, gate_ld a
+// multiple of 4; or null): the result is multiplied by gate_scale * sigmoid(gate[t, h * hd + d]) before it is rounded.
 HK_API int hk_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                    int table_stride, const void* items, int n_items, void* out, int H, int G, int hd,
                                    int page_tokens, int window, float scale_log2, int pages_cap, int* status, int sink,
-                                   const float* sinks, float softcap, int chunk, void* stream) {
+                                   const float* sinks, float softcap, int chunk, const float* gate, long long gate_ld,
+                                   float gate_scale, void* stream) {
   if (n_items <= 0) return 0;
-  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk);
+  if (gate != nullptr && ((((uintptr_t)gate) & 15) != 0 || (gate_ld & 3) != 0 || gate_ld < (long long)H * hd)) return HK_ERR_UNSUPPORTED;
+  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk, gate, gate_ld, gate_scale);
   if (G < 1 || H % G != 0 || (H / G) > ROWS || G > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
   if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
@@ -954,9 +975,11 @@ HK_API int hk_attention_prefill_tc(const void* q, const void* k_pages, const voi
 HK_API int hk_attention_prefill_tc2(const void* q, const void* k_pages, const void* v_pages, long long num_pages,
                                     const int* block_table, int table_stride, const void* items, int n_items, void* out, int H,
                                     int G, int hd, int page_tokens, int window, float scale_log2, int pages_cap, int* status,
-                                    int sink, const float* sinks, float softcap, int chunk, void* stream) {
+                                    int sink, const float* sinks, float softcap, int chunk, const float* gate, long long gate_ld,
+                                    float gate_scale, void* stream) {
   if (n_items <= 0) return 0;
-  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk);
+  if (gate != nullptr && ((((uintptr_t)gate) & 15) != 0 || (gate_ld & 3) != 0 || gate_ld < (long long)H * hd)) return HK_ERR_UNSUPPORTED;
+  const ScoreOpts so = make_opts(sink, sinks, softcap, scale_log2, chunk, gate, gate_ld, gate_scale);
   if (G < 1 || H % G != 0 || (H / G) > ROWS || G > 65535 || page_tokens < 1 || !(scale_log2 > 0.f)) return HK_ERR_UNSUPPORTED;
   if (hd != 64 && hd != 128) return HK_ERR_UNSUPPORTED;
   const bool boxes_ok = (page_tokens % 8 == 0 && TK % page_tokens == 0) || page_tokens % TK == 0;

@@ -367,9 +367,11 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, slot_of_token, 
     choice = _forced["attention"]
     if q.dtype == torch.bfloat16 and choice != "generic" and plan is not None and v_pages is not None and vd == hd:
         from . import attention_fast
-        if attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan,
-                              allow_tma=choice != "flash_cp", sink=sink, sinks=sinks, softcap=softcap, chunk=chunk):
-            if gate is not None:
+        done = attention_fast.run(q, k_pages, v_pages, block_table, out, H, G, hd, page_tokens, window, scale, plan,
+                                  allow_tma=choice != "flash_cp", sink=sink, sinks=sinks, softcap=softcap, chunk=chunk,
+                                  gate=gate, gate_scale=gate_scale)
+        if done:
+            if gate is not None and done != attention_fast.GATED:
                 sigmoid_gate(out, gate, out, gate_scale)
             return
         if choice is not None:
