@@ -67,7 +67,7 @@ class MifolornDelta:
         kv_heads = opt_int(raw, "kv_heads", heads)
         if heads % kv_heads:
             raise ConfigError(f"config.json {where}'heads' = {heads} is not a multiple of 'kv_heads' = {kv_heads}")
-        return cls(heads, kv_heads, dim, opt_int(raw, "vdim", dim), need_int(raw, "conv", minimum=2))
+        return cls(heads, kv_heads, dim, opt_int(raw, "vdim", dim), need_int(raw, "conv", minimum=1))
 
     def to_dict(self) -> dict:
         return {"conv": self.conv, "dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads, "vdim": self.vdim}

@@ -643,14 +643,15 @@ def mingru_scan(proj, z_bias, x_bias, segments, state, out) -> None:
 def short_conv(x, weight, segments, tail, out) -> None:
     """out[t, c] = silu(sum_j weight[c, j] * x[t - (taps - 1) + j, c]) over the rows of every segment (the last column
     of `weight` is the current token's).  Rows before a segment's first come from `tail` float32 [slots, taps - 1, C],
-    the request's last taps - 1 inputs (zero at its start), which is moved on.  x and out: float32 column slices [n, C]."""
+    the request's last taps - 1 inputs (zero at its start), which is moved on (with one tap: one row that is left alone).
+    x and out: float32 column slices [n, C]."""
     C = int(weight.shape[0])
     ldx, ldy = _cols(x, "x", C), _cols(out, "out", C)
     _need(weight, "weight", torch.float32, 2)
     _need(segments, "segments", torch.int32, 2)
     _need(tail, "tail", torch.float32, 3)
     taps = int(weight.shape[1])
-    if x.shape[0] != out.shape[0] or tuple(tail.shape[1:]) != (taps - 1, C) or segments.shape[1] != 3 or taps < 2:
+    if x.shape[0] != out.shape[0] or tuple(tail.shape[1:]) != (max(taps - 1, 1), C) or segments.shape[1] != 3 or taps < 1:
         raise KernelError("short_conv: shapes do not fit")
     lib = build.load("recurrent")
     _check(lib.hk_short_conv(_ptr(x), ctypes.c_longlong(ldx), _ptr(weight), _ptr(segments), int(segments.shape[0]), int(x.shape[0]),

@@ -180,8 +180,8 @@ class GatedDeltaRule(_SegmentScan):
                  names: Optional[Dict[str, str]] = None):
         if n_heads % kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {kv_heads} query/key heads")
-        if taps < 2:
-            raise ValueError("the short convolution needs at least two taps")
+        if taps < 1:
+            raise ValueError("the short convolution needs at least one tap")
         self.hidden, self.H, self.G, self.dk, self.dv, self.taps = hidden, n_heads, kv_heads, key_dim, value_dim, int(taps)
         self.prefix, self.norm_eps, self.unit_eps = prefix, float(norm_eps), float(unit_eps)
         self.q_scale = float(q_scale) if q_scale is not None else key_dim ** -0.5
@@ -209,7 +209,8 @@ class GatedDeltaRule(_SegmentScan):
         }
 
     def cache_specs(self):
-        return [StateSpec((self.H, self.dk, self.dv), torch.float32), StateSpec((self.taps - 1, self.channels), torch.float32)]
+        # one tap keeps no inputs; its tail is a row that nobody reads (a state of no size has no slot to live in)
+        return [StateSpec((self.H, self.dk, self.dv), torch.float32), StateSpec((max(self.taps - 1, 1), self.channels), torch.float32)]
 
     def own_bind(self, tensors, precision: Precision) -> None:
         p, nm = self.prefix, self.names

@@ -30,7 +30,7 @@ def test_configuration_round_trip_and_errors():
             config_from_dict(raw)
     broken(lambda r: r["layers"][0].__setitem__("type", "conv"))
     broken(lambda r: r["layers"][1]["mixer"]["left"].__setitem__("kv_heads", 3))
-    broken(lambda r: r["layers"][0]["mixer"].__setitem__("conv", 1))
+    broken(lambda r: r["layers"][0]["mixer"].__setitem__("conv", 0))
     broken(lambda r: r["layers"][2]["mixer"].__setitem__("gate_cap", 0))
     broken(lambda r: r["loop"].__setitem__("stop", 9))
     broken(lambda r: r["norm"].__setitem__("eps", 0))

@@ -67,7 +67,7 @@ def under_every_cut(part, prec, dtype, lengths, plain, std_in=1.0):
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("d,H,G,dk,dv,taps", [(40, 2, 1, 16, 8, 4), (24, 3, 3, 8, 12, 2), (72, 1, 1, 64, 64, 3), (48, 4, 2, 40, 20, 5),
-                                              (32, 2, 2, 136, 6, 4), (24, 6, 2, 6, 7, 3), (32, 4, 4, 32, 32, 7)])
+                                              (32, 2, 2, 136, 6, 4), (24, 6, 2, 6, 7, 3), (32, 4, 4, 32, 32, 7), (24, 2, 1, 8, 12, 1)])
 def test_gated_delta_rule_under_every_cut(dtype, d, H, G, dk, dv, taps):
     from hk_b200.parts import GatedDeltaRule
     part = GatedDeltaRule(d, H, G, dk, dv, taps, "m.", norm_eps=1e-5)
