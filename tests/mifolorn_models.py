@@ -71,8 +71,19 @@ CONFIGS = {
                                    delta(4, 2, 32, 16, 4), 0.9, 1.2), 160),
         layer("mlstm", mlstm(2, 32, 64, 10.0), 96),
     ], 0.08, scale=2.0, side=16, loop=(0, 2, 2)),
+    # sizes that no vector load divides: a width of 8 * 5, feed-forwards of 4 * 13 and 2 * 15, a token input of 5, an odd
+    # vocabulary, six rotated dims, key and value sizes of 12 / 10 / 20 / 28 / 36, a head wider than 128, a convolution of
+    # one tap; the loop covers the first two layers and the last layer has no feed-forward
+    "X": config(40, 103, 1e-6, [
+        layer("parallel", parallel(attention(3, 1, 24, 40, 0.25, {"base": 10000.0, "dims": 6, "scaling": YARN}, 10.0),
+                                   delta(3, 1, 20, 28, 3), 1.0, 1.0), 52),
+        layer("mlstm", mlstm(3, 20, 36, 6.0), 30),
+        layer("delta", delta(6, 2, 12, 10, 2), 44),
+        layer("parallel", parallel(attention(2, 2, 136, 72, 0.09, {"base": 3000.0, "dims": 136, "scaling": YARN}, 60.0),
+                                   delta(1, 1, 72, 40, 1), 2.0, 0.25), None),
+    ], 0.15, scale=3.0, side=5, loop=(0, 2, 2)),
 }
-SEEDS = {"U": 31, "V": 32, "W": 33}
+SEEDS = {"U": 31, "V": 32, "W": 33, "X": 34}
 
 
 def make_model_dir(tmpdir, which: str, dtype=torch.float32) -> str:

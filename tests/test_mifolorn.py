@@ -36,7 +36,7 @@ def test_configuration_round_trip_and_errors():
     broken(lambda r: r["norm"].__setitem__("eps", 0))
 
 
-@pytest.mark.parametrize("which", ["U", "V", "W"])
+@pytest.mark.parametrize("which", ["U", "V", "W", "X"])
 def test_schedule_and_declared_tensors(which):
     from hk_b200.config import config_from_dict
     from hk_b200.models.mifolorn import build_mifolorn

@@ -33,6 +33,7 @@ CASES = {
     "U": dict(lengths=[7, 30, 61, 2, 45], page_tokens=4),
     "V": dict(lengths=[90, 5, 33, 140], page_tokens=16),
     "W": dict(lengths=[150, 20, 75, 210], page_tokens=16),
+    "X": dict(lengths=[66, 3, 131, 40], page_tokens=8),
 }
 _cache = {}
 
@@ -100,7 +101,7 @@ def check(got, cfg, weights, seqs, ref, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
-@pytest.mark.parametrize("which", ["U", "V", "W"])
+@pytest.mark.parametrize("which", ["U", "V", "W", "X"])
 @pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed", "mixed_tight"])
 def test_replay_matches_plain(tmp_path_factory, which, dtype, family):
     from hk_b200.engine import Engine
