@@ -488,14 +488,19 @@ HK_API int hk_add_bias(float* out, const float* bias, int n, int N, void* stream
 // ----------------------------------------------------------------------------- swiglu
 // out[t, j] = silu(gate_j) * up_j for the fused projection gu[n, 2F], laid out in blocks of
 // `block` gates followed by the matching `block` ups (block == F: all gates, then all ups).
-// `act` chooses the gate's activation: 0 = silu (SwiGLU), 1 = the tanh form of gelu (GeGLU).
-__device__ __forceinline__ float glu_act(float g, int act) {
-  if (act == 0) return g / (1.0f + expf(-g));
-  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+// `act` chooses the gate's activation: 0 = silu (SwiGLU), 1 = the tanh form of gelu (GeGLU), 2 = the clamped form
+// min(g, p0) * sigmoid(p1 * min(g, p0)) * (clamp(u, -p0, p0) + 1) with the limit p0 and the sigmoid's slope p1.
+__device__ __forceinline__ float glu_pair(float g, float u, int act, float p0, float p1) {
+  if (act == 0) return g / (1.0f + expf(-g)) * u;
+  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  g = fminf(g, p0);
+  u = fminf(fmaxf(u, -p0), p0);
+  return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
 }
 
 template <typename TO>
-__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block, int act) {
+__global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int F, int block, int act,
+                              float p0, float p1) {
   pdl_launch_dependents();
   pdl_wait();
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -505,17 +510,17 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, TO* __restrict__ out
   long long gi = t * 2 * F + (long long)(j / block) * 2 * block + (j % block);
   float g = gu[gi];
   float u = gu[gi + block];
-  out[i] = from_f32<TO>(glu_act(g, act) * u);
+  out[i] = from_f32<TO>(glu_pair(g, u, act, p0, p1));
 }
 
-HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, int block, int act, void* stream) {
+HK_API int hk_swiglu(const float* gu, void* out, int out_dtype, int n, int F, int block, int act, float p0, float p1, void* stream) {
   if (n <= 0) return 0;
-  if (block <= 0 || F % block || act < 0 || act > 1) return HK_ERR_UNSUPPORTED;
+  if (block <= 0 || F % block || act < 0 || act > 2) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   long long total = (long long)n * F;
   unsigned blocks = (unsigned)((total + 255) / 256);
-  if (out_dtype == HK_F32) return hk_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, gu, (float*)out, total, F, block, act);
-  if (out_dtype == HK_BF16) return hk_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, gu, (bf16*)out, total, F, block, act);
+  if (out_dtype == HK_F32) return hk_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, s, gu, (float*)out, total, F, block, act, p0, p1);
+  if (out_dtype == HK_BF16) return hk_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, s, gu, (bf16*)out, total, F, block, act, p0, p1);
   return HK_ERR_UNSUPPORTED;
 }
 
@@ -973,5 +978,129 @@ HK_API int hk_token_gate(const float* z, long long ld, const void* table, int ta
   if (table_dtype == HK_F32 && out_dtype == HK_BF16)
     return hk_launch(token_gate_kernel<float, bf16>, grid, block, 0, s, z, ld, (const float*)table, table_cols, col0, ids, (bf16*)out,
                      total, W, act);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// ----------------------------------------------------------------------------- attention with several score maps per head
+// An attention whose heads carry M score maps over the same values (M = 2: a differential attention) runs on the
+// ordinary paged attention kernels as H * M query heads over G key/value heads: a key/value head's cache row is the
+// M maps' keys side by side [M * dk], and query head (h, j) is map j's query at its place in a row of M * dk numbers
+// that is zero elsewhere, so its score with the row is q_j . k_j and every map of a head reads the same value.
+// This kernel turns the projected (and convolved) float32 row x = [H * M * dk q | G * M * dk k | G * vd v] of every
+// token into that layout: q and k are turned by position on the first `rot` dims of every map (dim i paired with
+// i + rot / 2), the queries are written to q_out [n, H * M, M * dk], keys and values to the token's place in its pages
+// [page, G, page_tokens, M * dk] and [page, G, page_tokens, vd].  One warp per (token, unit); a unit is a query map,
+// a key map or a value head.
+template <typename T>
+__global__ void __launch_bounds__(128)
+maps_rope_kv_write_kernel(const float* __restrict__ x, long long ld, T* __restrict__ q_out, const float* __restrict__ cos_t,
+                          const float* __restrict__ sin_t, int rot, const int* __restrict__ positions,
+                          const int* __restrict__ slot_of_token, const int* __restrict__ block_table, int table_stride,
+                          T* __restrict__ k_pages, T* __restrict__ v_pages, int n, int H, int G, int M, int dk, int vd,
+                          int page_tokens, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int qu = H * M, ku = G * M;
+  const int units = qu + (write_kv ? ku + G : 0);
+  const long long item = (long long)blockIdx.x * 4 + wid;
+  if (item >= (long long)n * units) return;
+  const int t = (int)(item / units), u = (int)(item % units);
+  const int pos = positions[t];
+  const float* row = x + (size_t)t * ld;
+  const int half = rot >> 1;
+  const float* c = cos_t + (size_t)pos * half;
+  const float* s = sin_t + (size_t)pos * half;
+  size_t cache_at = 0;
+  if (u >= qu) {
+    const int page = block_table[(size_t)slot_of_token[t] * table_stride + pos / page_tokens];
+    if (page < 0) return;   // the host never schedules this; keeps a stale table from writing out of bounds
+    const int g = u < qu + ku ? (u - qu) / M : u - qu - ku;
+    cache_at = ((size_t)page * G + g) * page_tokens + (pos % page_tokens);
+  }
+  if (u >= qu + ku) {       // a value head: copied
+    const float* src = row + (size_t)(qu + ku) * dk + (size_t)(u - qu - ku) * vd;
+    T* dst = v_pages + cache_at * vd;
+    for (int i = lane; i < vd; i += 32) dst[i] = from_f32<T>(src[i]);
+    return;
+  }
+  const float* src = row + (size_t)u * dk;       // q maps and k maps follow one another in x
+  const int j = u % M;
+  T* dst = u < qu ? q_out + ((size_t)t * qu + u) * M * dk : k_pages + cache_at * M * dk;
+  if (u < qu)               // a query row is zero outside its own map
+    for (int i = lane; i < M * dk; i += 32)
+      if (i / dk != j) dst[i] = from_f32<T>(0.f);
+  dst += (size_t)j * dk;
+  for (int i = lane; i < dk; i += 32) {
+    float v;
+    if (i < half) v = src[i] * c[i] - src[i + half] * s[i];
+    else if (i < rot) v = src[i] * c[i - half] + src[i - half] * s[i - half];
+    else v = src[i];
+    dst[i] = from_f32<T>(v);
+  }
+}
+
+HK_API int hk_maps_rope_kv_write(const float* x, long long ld, void* q_out, int dtype, const float* cos_t, const float* sin_t, int rot,
+                                 const int* positions, const int* slot_of_token, const int* block_table, int table_stride,
+                                 void* k_pages, void* v_pages, int n, int H, int G, int M, int dk, int vd, int page_tokens,
+                                 int write_kv, void* stream) {
+  if (n <= 0) return 0;
+  if (rot < 0 || rot > dk || (rot & 1) || H < 1 || G < 1 || M < 1 || dk < 1 || vd < 1) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long items = (long long)n * (H * M + (write_kv ? G * M + G : 0));
+  const dim3 grid((unsigned)((items + 3) / 4)), block(128);
+  if (dtype == HK_F32)
+    return hk_launch_pdl(maps_rope_kv_write_kernel<float>, grid, block, 0, s, x, ld, (float*)q_out, cos_t, sin_t, rot, positions,
+                         slot_of_token, block_table, table_stride, (float*)k_pages, (float*)v_pages, n, H, G, M, dk, vd, page_tokens,
+                         write_kv);
+  if (dtype == HK_BF16)
+    return hk_launch_pdl(maps_rope_kv_write_kernel<bf16>, grid, block, 0, s, x, ld, (bf16*)q_out, cos_t, sin_t, rot, positions,
+                         slot_of_token, block_table, table_stride, (bf16*)k_pages, (bf16*)v_pages, n, H, G, M, dk, vd, page_tokens,
+                         write_kv);
+  return HK_ERR_UNSUPPORTED;
+}
+
+// The heads' outputs of a differential attention: with a1 = a[t, 2h] and a2 = a[t, 2h + 1] the two maps' weighted values,
+//     o = a1 - lambda * a2;   out[t, h] = o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate[t, h])
+// (gate: float32 logits, one per head, row stride ldg; null: no gate).  One warp per (token, head), float32 arithmetic.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+diff_heads_out_kernel(const TI* __restrict__ a, const float* __restrict__ gate, long long ldg, TO* __restrict__ out, long long items,
+                      int H, int vd, float lambda, float eps, float out_scale) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const long long t = item / H;
+  const int h = (int)(item % H);
+  const TI* a1 = a + (size_t)item * 2 * vd;
+  const TI* a2 = a1 + vd;
+  float ss = 0.f;
+  for (int i = lane; i < vd; i += 32) {
+    const float o = fmaf(-lambda, to_f32<TI>(a2[i]), to_f32<TI>(a1[i]));
+    ss = fmaf(o, o, ss);
+  }
+  ss = warp_sum(ss);
+  float f = out_scale / sqrtf(ss / (float)vd + eps);
+  if (gate != nullptr) f /= 1.0f + expf(-gate[(size_t)t * ldg + h]);
+  for (int i = lane; i < vd; i += 32)
+    out[(size_t)item * vd + i] = from_f32<TO>(fmaf(-lambda, to_f32<TI>(a2[i]), to_f32<TI>(a1[i])) * f);
+}
+
+HK_API int hk_diff_heads_out(const void* a, int a_dtype, const float* gate, long long ldg, void* out, int out_dtype, int n, int H,
+                             int vd, float lambda, float eps, float out_scale, void* stream) {
+  if (n <= 0) return 0;
+  if (H < 1 || vd < 1) return HK_ERR_UNSUPPORTED;
+  const long long items = (long long)n * H;
+  const dim3 grid((unsigned)((items + 7) / 8)), block(256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (a_dtype == HK_F32 && out_dtype == HK_F32)
+    return hk_launch(diff_heads_out_kernel<float, float>, grid, block, 0, s, (const float*)a, gate, ldg, (float*)out, items, H, vd,
+                     lambda, eps, out_scale);
+  if (a_dtype == HK_BF16 && out_dtype == HK_BF16)
+    return hk_launch(diff_heads_out_kernel<bf16, bf16>, grid, block, 0, s, (const bf16*)a, gate, ldg, (bf16*)out, items, H, vd,
+                     lambda, eps, out_scale);
+  if (a_dtype == HK_F32 && out_dtype == HK_BF16)
+    return hk_launch(diff_heads_out_kernel<float, bf16>, grid, block, 0, s, (const float*)a, gate, ldg, (bf16*)out, items, H, vd,
+                     lambda, eps, out_scale);
   return HK_ERR_UNSUPPORTED;
 }

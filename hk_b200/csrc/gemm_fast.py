@@ -221,10 +221,12 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
     return True
 
 
-def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None, act: int = 0) -> bool:
+def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None, act: int = 0, limit: float = 0.0, slope: float = 1.0) -> bool:
     """out (bf16 [M, F]) = act(gate) * up of a w^T for w = [F gate rows | F up rows], in the epilogue of the
     streaming kernel (few rows) or of the tcgen05 kernel; act 0 is silu, 1 the tanh form of gelu.  False when they
-    refuse."""
+    refuse (the clamped form, act 2, is not fused: the caller runs the product and the activation kernel)."""
+    if act not in (0, 1):
+        return False
     epilogue = 2 + int(act)
     from . import ops
     M, K = a.shape

@@ -160,14 +160,16 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
 # ---- swiglu ---------------------------------------------------------------------------
 
 
-GLU_ACTS = {"silu": 0, "gelu_tanh": 1}
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, act: str = "silu") -> None:
-    """out[t, j] = act(gate) * up for gate_up float32 [n, 2F]; act is silu or the tanh form of gelu.  With block = 0
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, act: str = "silu", limit: float = 0.0,
+           slope: float = 1.0) -> None:
+    """out[t, j] = act(gate) * up for gate_up float32 [n, 2F]; act is silu or the tanh form of gelu; or, with act
+    'swish_clamped', g sigmoid(slope g) (u + 1) with g = min(gate, limit) and u = clamp(up, -limit, limit).  With block = 0
     the row is laid out [F gates | F ups]; with block = b (dividing F) it is [b gates | b ups | b gates | ...]."""
     if act not in GLU_ACTS:
-        raise KernelError(f"swiglu: activation {act!r} is neither 'silu' nor 'gelu_tanh'")
+        raise KernelError(f"swiglu: activation {act!r} is not one of {', '.join(GLU_ACTS)}")
     _need(gate_up, "gate_up", torch.float32, 2)
     _need(out, "out", dims=2)
     n, f = out.shape
@@ -175,7 +177,8 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, act: str = 
     if gate_up.shape[0] != n or gate_up.shape[1] != 2 * f or f % block:
         raise KernelError("swiglu: gate_up must be [n, 2F] for out [n, F], and the block must divide F")
     lib = build.load("elementwise")
-    _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, int(block), GLU_ACTS[act], _stream()), "swiglu")
+    _check(lib.hk_swiglu(_ptr(gate_up), _ptr(out), _dt(out), n, f, int(block), GLU_ACTS[act], ctypes.c_float(limit),
+                         ctypes.c_float(slope), _stream()), "swiglu")
 
 
 def _as_weights(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -188,8 +191,10 @@ def _as_weights(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return a.to(w.dtype)
 
 
-def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu") -> None:
-    """out[M, F] = act(gate) * up (act: silu, or the tanh form of gelu) of a @ w_gate_up^T, w_gate_up [2F, K] = [F gate rows | F up rows].  Fused into
+def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, act: str = "silu", limit: float = 0.0,
+                slope: float = 1.0) -> None:
+    """out[M, F] = act(gate) * up (act: silu, the tanh form of gelu, or the clamped form of `swiglu` with its limit and
+    slope) of a @ w_gate_up^T, w_gate_up [2F, K] = [F gate rows | F up rows].  Fused into
     the tensor-core product's epilogue when that takes the shape (a tile of the product then holds gate rows and
     the up rows that match them), else a product to float32 followed by the swiglu kernel."""
     _need(a, "a", dims=2)
@@ -197,7 +202,7 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, act
     _need(out, "out", a.dtype, 2)
     if w_gate_up.dtype != a.dtype:              # weights kept in 32-bit on the bfloat16 path: this product runs in 32-bit
         wide = torch.empty(out.shape, dtype=w_gate_up.dtype, device=out.device)
-        gemm_swiglu(_as_weights(a, w_gate_up), w_gate_up, wide, act)
+        gemm_swiglu(_as_weights(a, w_gate_up), w_gate_up, wide, act, limit, slope)
         out.copy_(wide)
         return
     M, F = out.shape
@@ -205,11 +210,11 @@ def gemm_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, act
         raise KernelError("gemm_swiglu: shapes do not fit")
     if a.dtype == torch.bfloat16 and _forced["gemm"] in (None, "tc", "stream"):
         from . import gemm_fast
-        if gemm_fast.run_swiglu(a, w_gate_up, out, _forced["gemm"], act=GLU_ACTS[act]):
+        if gemm_fast.run_swiglu(a, w_gate_up, out, _forced["gemm"], act=GLU_ACTS[act], limit=limit, slope=slope):
             return
     gu = torch.empty((M, 2 * F), dtype=torch.float32, device=a.device)
     gemm(a, w_gate_up, gu)
-    swiglu(gu, out, 0, act)
+    swiglu(gu, out, 0, act, limit, slope)
 
 
 # ---- per-head norm + rotation + cache write ---------------------------------------------
@@ -274,6 +279,58 @@ def qk_norm_rope_kv_write(qkv, q_out, q_weight, k_weight, eps, cos, sin, rotary_
         _ptr(v_pages if write_kv else None), n, H, G, hd, int(page_tokens), 1 if write_kv else 0, _ptr(bias),
         PAIRINGS[pairing], 1 if norm_after else 0, 1 if tied_v else 0, vd, ctypes.c_longlong(qkv.stride(0)), _stream()),
         "qk_norm_rope_kv_write")
+
+
+def maps_rope_kv_write(x, q_out, cos, sin, rotary_dim: int, positions, slot_of_token, block_table, k_pages, v_pages,
+                       n_heads: int, n_kv_heads: int, maps: int, key_dim: int, page_tokens: int, write_kv: bool = True) -> None:
+    """For an attention whose heads carry `maps` score maps over the same values: splits the float32 row
+    x[n, H*maps*dk | G*maps*dk | G*vd] (a column slice), turns q and k by position on the first `rotary_dim` dims of
+    every map (dim i paired with i + rotary_dim/2), writes the queries as H*maps heads of maps*dk numbers (a map's query at
+    its own place, zeros elsewhere) to q_out[n, H*maps*maps*dk] and the keys (a head's maps side by side) and values into
+    the token's place in k_pages [pages, G, page_tokens, maps*dk] and v_pages [pages, G, page_tokens, vd]."""
+    H, G, M, dk = n_heads, n_kv_heads, maps, key_dim
+    _need(q_out, "q_out", dims=2)
+    _need(v_pages, "v_pages", q_out.dtype, 4)
+    _need(k_pages, "k_pages", q_out.dtype, 4)
+    vd = int(v_pages.shape[3])
+    ld = _cols(x, "x", (H + G) * M * dk + G * vd)
+    n = x.shape[0]
+    if tuple(q_out.shape) != (n, H * M * M * dk) or tuple(k_pages.shape[1:]) != (G, page_tokens, M * dk) \
+            or tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3]):
+        raise KernelError("maps_rope_kv_write: shapes do not fit")
+    if rotary_dim > 0:
+        _need(cos, "cos", torch.float32, 2)
+        _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape or rotary_dim % 2 or rotary_dim > dk:
+            raise KernelError("maps_rope_kv_write: rotation tables must be [positions, rotary_dim/2]")
+    _need(positions, "positions", torch.int32, 1)
+    _need(slot_of_token, "slot_of_token", torch.int32, 1)
+    _need(block_table, "block_table", torch.int32, 2)
+    lib = build.load("elementwise")
+    _check(lib.hk_maps_rope_kv_write(
+        _ptr(x), ctypes.c_longlong(ld), _ptr(q_out), _dt(q_out), _ptr(cos if rotary_dim > 0 else None),
+        _ptr(sin if rotary_dim > 0 else None), int(rotary_dim), _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
+        int(block_table.shape[1]), _ptr(k_pages), _ptr(v_pages), n, H, G, M, dk, vd, int(page_tokens), 1 if write_kv else 0,
+        _stream()), "maps_rope_kv_write")
+
+
+def diff_heads_out(a, gate, out, n_heads: int, value_dim: int, lam: float, eps: float, out_scale: float = 1.0) -> None:
+    """The heads of a differential attention: a[n, H*2*vd] holds, per head, the two maps' weighted values a1 | a2;
+    o = a1 - lam * a2, out[t, h] = o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate[t, h]) (gate: a float32 column slice
+    [n, H], or None).  a float32 or out's type; float32 arithmetic."""
+    H, vd = n_heads, value_dim
+    _need(a, "a", dims=2)
+    _need(out, "out", dims=2)
+    n = out.shape[0]
+    ldg = 0
+    if gate is not None:
+        ldg = _cols(gate, "gate", H)
+    if tuple(a.shape) != (n, 2 * H * vd) or tuple(out.shape) != (n, H * vd) or (gate is not None and gate.shape[0] != n) \
+            or (a.dtype != torch.float32 and a.dtype != out.dtype):
+        raise KernelError("diff_heads_out: shapes or types do not fit")
+    lib = build.load("elementwise")
+    _check(lib.hk_diff_heads_out(_ptr(a), _dt(a), _ptr(gate), ctypes.c_longlong(ldg), _ptr(out), _dt(out), n, H, vd,
+                                 ctypes.c_float(lam), ctypes.c_float(eps), ctypes.c_float(out_scale), _stream()), "diff_heads_out")
 
 
 # ---- matrix product -------------------------------------------------------------------
@@ -640,9 +697,9 @@ def mingru_scan(proj, z_bias, x_bias, segments, state, out) -> None:
                               int(segments.shape[0]), _ptr(state), _ptr(out), _dt(out), W, _stream()), "mingru_scan")
 
 
-def short_conv(x, weight, segments, tail, out) -> None:
-    """out[t, c] = silu(sum_j weight[c, j] * x[t - (taps - 1) + j, c]) over the rows of every segment (the last column
-    of `weight` is the current token's).  Rows before a segment's first come from `tail` float32 [slots, taps - 1, C],
+def short_conv(x, weight, segments, tail, out, act: str = "silu") -> None:
+    """out[t, c] = act(sum_j weight[c, j] * x[t - (taps - 1) + j, c]) over the rows of every segment (the last column
+    of `weight` is the current token's); act 'silu' or 'none'.  Rows before a segment's first come from `tail` float32 [slots, taps - 1, C],
     the request's last taps - 1 inputs (zero at its start), which is moved on (with one tap: one row that is left alone).
     x and out: float32 column slices [n, C]."""
     C = int(weight.shape[0])
@@ -651,11 +708,13 @@ def short_conv(x, weight, segments, tail, out) -> None:
     _need(segments, "segments", torch.int32, 2)
     _need(tail, "tail", torch.float32, 3)
     taps = int(weight.shape[1])
-    if x.shape[0] != out.shape[0] or tuple(tail.shape[1:]) != (max(taps - 1, 1), C) or segments.shape[1] != 3 or taps < 1:
+    if x.shape[0] != out.shape[0] or tuple(tail.shape[1:]) != (max(taps - 1, 1), C) or segments.shape[1] != 3 or taps < 1 \
+            or act not in ("silu", "none"):
         raise KernelError("short_conv: shapes do not fit")
     lib = build.load("recurrent")
     _check(lib.hk_short_conv(_ptr(x), ctypes.c_longlong(ldx), _ptr(weight), _ptr(segments), int(segments.shape[0]), int(x.shape[0]),
-                             _ptr(tail), _ptr(out), ctypes.c_longlong(ldy), C, taps, _stream()), "short_conv")
+                             _ptr(tail), _ptr(out), ctypes.c_longlong(ldy), C, taps, 1 if act == "silu" else 0, _stream()),
+           "short_conv")
 
 
 def gated_delta_scan(q, k, v, b_logit, a_logit, a_log, dt_bias, segments, state, out, n_heads: int, n_qk_heads: int,
@@ -687,6 +746,39 @@ def gated_delta_scan(q, k, v, b_logit, a_logit, a_log, dt_bias, segments, state,
                                    ctypes.c_longlong(ldg), _ptr(a_log), _ptr(dt_bias), _ptr(segments), int(segments.shape[0]), n,
                                    _ptr(rec), _ptr(state), _ptr(out), H, G, dk, dv, ctypes.c_float(q_scale),
                                    ctypes.c_float(unit_eps), _stream()), "gated_delta_scan", launches=2)
+
+
+def retention_scan(q, k, v, cos, sin, rotary_dim: int, positions, decay, segments, state, out, n_heads: int, key_dim: int,
+                   value_dim: int, k_scale: float) -> None:
+    """Retention over the rows of every segment, per head, S = state[slot, head] float32 [dk, dv]:
+        S <- decay[h] S + k v^T;  out = S^T q
+    with q and k turned by position on their first `rotary_dim` dims (dim i paired with i + rotary_dim / 2; tables
+    cos, sin float32 [positions, rotary_dim / 2]; 0: no rotation) and k then times k_scale.  q, k [n, H*dk] and v
+    [n, H*dv]: float32 column slices of ONE matrix; decay float32 [H]; out float32 [n, H*dv]."""
+    H, dk, dv = n_heads, key_dim, value_dim
+    ld = _cols(q, "q", H * dk)
+    if _cols(k, "k", H * dk) != ld or _cols(v, "v", H * dv) != ld:
+        raise KernelError("retention_scan: q, k and v must be slices of one matrix")
+    _need(decay, "decay", torch.float32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    _need(segments, "segments", torch.int32, 2)
+    _need(state, "state", torch.float32, 4)
+    _need(out, "out", torch.float32, 2)
+    n = q.shape[0]
+    if rotary_dim > 0:
+        _need(cos, "cos", torch.float32, 2)
+        _need(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape or rotary_dim % 2 or rotary_dim > dk:
+            raise KernelError("retention_scan: rotation tables must be [positions, rotary_dim/2]")
+    if tuple(state.shape[1:]) != (H, dk, dv) or tuple(out.shape) != (n, H * dv) or segments.shape[1] != 3 \
+            or decay.shape[0] != H or positions.shape[0] != n:
+        raise KernelError("retention_scan: shapes do not fit")
+    lib = build.load("recurrent")
+    rec = torch.empty(n * H * int(lib.hk_delta_rule_record(dk, dv)), dtype=torch.float32, device=out.device)
+    _check(lib.hk_retention_scan(_ptr(q), _ptr(k), _ptr(v), ctypes.c_longlong(ld), _ptr(cos if rotary_dim > 0 else None),
+                                 _ptr(sin if rotary_dim > 0 else None), int(rotary_dim), _ptr(positions), _ptr(decay), _ptr(segments),
+                                 int(segments.shape[0]), n, _ptr(rec), _ptr(state), _ptr(out), H, dk, dv, ctypes.c_float(k_scale),
+                                 _stream()), "retention_scan", launches=2)
 
 
 def mlstm_padded(value_dim: int) -> int:
@@ -730,16 +822,17 @@ def mlstm_scan(q, k, v, i_logit, f_logit, i_bias, f_bias, segments, state, m_sta
 def head_out_gate(o, gate_logit, weight, eps: float, out, n_heads: int, value_dim: int, act: str = "sigmoid",
                   gates=None, den_eps: float = 0.0) -> None:
     """out[t, h, :] = N(o[t, h, :dv] / den) * weight * act(gate_logit[t, h, :]), N = x / sqrt(mean(x^2) + eps) over the
-    head's dv values.  o float32 [n, H*ldo] with ldo >= dv floats per head; weight [H*dv], or [dv] shared by the heads;
-    act 'sigmoid' or 'silu'.  With `gates` (float32 [n, H, 3], as `mlstm_scan` leaves it) den = max(|o[t, h, dv]|,
+    head's dv values.  o float32 [n, H*ldo] with ldo >= dv floats per head; weight [H*dv], or [dv] shared by the heads, or
+    None (a norm without a weight); act 'sigmoid' or 'silu'.  With `gates` (float32 [n, H, 3], as `mlstm_scan` leaves it) den = max(|o[t, h, dv]|,
     gates[t, h, 2]) + den_eps; without, den = 1."""
     H, dv = n_heads, value_dim
     _need(o, "o", torch.float32, 2)
     ldg = _cols(gate_logit, "gate_logit", H * dv)
-    _need(weight, "weight", torch.float32, 1)
+    if weight is not None:
+        _need(weight, "weight", torch.float32, 1)
     _need(out, "out", dims=2)
     n = out.shape[0]
-    if o.shape[0] != n or o.shape[1] % H or tuple(out.shape) != (n, H * dv) or weight.shape[0] not in (dv, H * dv) \
+    if o.shape[0] != n or o.shape[1] % H or tuple(out.shape) != (n, H * dv) or (weight is not None and weight.shape[0] not in (dv, H * dv)) \
             or gate_logit.shape[0] != n or act not in ("sigmoid", "silu"):
         raise KernelError("head_out_gate: shapes do not fit")
     ldo = o.shape[1] // H
@@ -747,7 +840,7 @@ def head_out_gate(o, gate_logit, weight, eps: float, out, n_heads: int, value_di
         _need(gates, "gates", torch.float32, 3)
         if tuple(gates.shape) != (n, H, 3):
             raise KernelError("head_out_gate: gates must be [n, H, 3]")
-    shared = 1 if (weight.shape[0] == dv and H > 1) else 0
+    shared = 1 if (weight is not None and weight.shape[0] == dv and H > 1) else 0
     lib = build.load("recurrent")
     _check(lib.hk_head_out_gate(_ptr(o), int(ldo), _ptr(gate_logit), ctypes.c_longlong(ldg), _ptr(weight), shared,
                                 0 if act == "sigmoid" else 1, _ptr(gates), ctypes.c_float(den_eps), _ptr(out), _dt(out), n, H, dv,
@@ -804,19 +897,37 @@ def route_tile_rows() -> int:
     return int(build.load("routed").hk_route_tile_rows())
 
 
-def route_topk(x, w_router, ids, weights) -> None:
+def route_topk(x, w_router, ids, weights, scores: str = "softmax", correction=None, groups: int = 0, keep: int = 0,
+               scale: float = 1.0, norm_eps: float = 0.0, extra_out=None) -> None:
     """Per row of x [n, d]: the `top` = ids.shape[1] largest of the E float32 router logits x . w_router[e]
-    (w_router float32 [E, d]; the lower index wins a tie), and the softmax over the chosen logits."""
+    (w_router float32 [E, d]; the lower index wins a tie), and the softmax over the chosen logits.
+    scores 'sigmoid': every expert's score is s = sigmoid(logit); the choice is made on s + correction (float32 [E], or
+    None), among the experts of the best `keep` of `groups` equal groups of neighbours when groups > 0 (a group's score: the
+    sum of its two largest choice scores; the others count as minus infinity); weights = s / (sum of the chosen s +
+    norm_eps) * scale.  `extra_out` float32 [n, X]: w_router has X more rows behind the experts', and the sigmoids of their
+    logits are written there."""
     _need(x, "x", dims=2)
     _need(w_router, "w_router", torch.float32, 2)
     _need(ids, "ids", torch.int32, 2)
     _need(weights, "weights", torch.float32, 2)
     n, d = x.shape
-    if w_router.shape[1] != d or ids.shape[0] != n or ids.shape != weights.shape:
+    extra = 0
+    if extra_out is not None:
+        _need(extra_out, "extra_out", torch.float32, 2)
+        extra = int(extra_out.shape[1])
+        if extra_out.shape[0] != n:
+            raise KernelError("route_topk: one row of extra_out per row of x")
+    E = int(w_router.shape[0]) - extra
+    if w_router.shape[1] != d or ids.shape[0] != n or ids.shape != weights.shape or scores not in ("softmax", "sigmoid") or E < 1:
         raise KernelError("route_topk: shapes do not fit")
+    if correction is not None:
+        _need(correction, "correction", torch.float32, 1)
+        if correction.shape[0] != E:
+            raise KernelError("route_topk: one correction per expert")
     lib = build.load("routed")
-    _check(lib.hk_route_topk(_ptr(x), _dt(x), _ptr(w_router), _ptr(ids), _ptr(weights), n, d, w_router.shape[0],
-                             ids.shape[1], _stream()), "route_topk")
+    _check(lib.hk_route_topk(_ptr(x), _dt(x), _ptr(w_router), _ptr(ids), _ptr(weights), n, d, E, ids.shape[1],
+                             1 if scores == "sigmoid" else 0, _ptr(correction), int(groups), int(keep), ctypes.c_float(scale),
+                             ctypes.c_float(norm_eps), extra, _ptr(extra_out), _stream()), "route_topk")
 
 
 def route_sort(ids, n_experts: int, offsets, perm, inv, tiles) -> None:
@@ -849,8 +960,9 @@ def grouped_gemm(a, w, out, tiles, offsets, perm, top: int, gather: bool, gated:
                                int(top), 1 if gather else 0, N, K, 1 if gated else 0, _stream()), "grouped_gemm")
 
 
-def route_combine(ys, inv, weights, y, accumulate: bool = False) -> None:
-    """y[t, :] (+)= sum_k weights[t, k] * ys[inv[t, k], :], the choices in their order (all float32)."""
+def route_combine(ys, inv, weights, y, accumulate: bool = False, shared=None, shared_gate=None) -> None:
+    """y[t, :] (+)= sum_k weights[t, k] * ys[inv[t, k], :], the choices in their order (all float32); with `shared`
+    (float32 [n, d]) also + shared_gate[t] * shared[t, :] (shared_gate float32 [n] or [n, 1]; None: 1)."""
     _need(ys, "ys", torch.float32, 2)
     _need(inv, "inv", torch.int32)
     _need(weights, "weights", torch.float32, 2)
@@ -858,9 +970,14 @@ def route_combine(ys, inv, weights, y, accumulate: bool = False) -> None:
     n, top = weights.shape
     if y.shape[0] != n or ys.shape[1] != y.shape[1] or inv.numel() != n * top or ys.shape[0] < n * top:
         raise KernelError("route_combine: shapes do not fit")
+    if shared is not None:
+        _need(shared, "shared", torch.float32, 2)
+        if shared.shape != y.shape or (shared_gate is not None and (shared_gate.dtype != torch.float32 or shared_gate.numel() != n
+                                                                    or not shared_gate.is_contiguous())):
+            raise KernelError("route_combine: the shared result must be [n, d] and its gate [n]")
     lib = build.load("routed")
     _check(lib.hk_route_combine(_ptr(ys), _ptr(inv), _ptr(weights), _ptr(y), n, y.shape[1], top, 1 if accumulate else 0,
-                                _stream()), "route_combine")
+                                _ptr(shared), _ptr(shared_gate if shared is not None else None), _stream()), "route_combine")
 
 
 def route_sort_padded(ids, n_experts: int, pad: int, perm, inv, groups) -> None:

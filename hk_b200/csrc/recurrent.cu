@@ -485,8 +485,8 @@ HK_API int hk_mingru_scan(const float* proj, long long ld, const float* z_bias, 
 }
 
 // ------------------------------------------------------------------ short causal convolution per channel
-// y[t, c] = act(sum_j w[c, j] * x[t - (taps - 1) + j, c]) over the rows of every segment, with act = silu: the last
-// column of w is the current token's.  The inputs before a segment's first row come from the request's tail
+// y[t, c] = act(sum_j w[c, j] * x[t - (taps - 1) + j, c]) over the rows of every segment, with act = silu (1) or the
+// identity (0): the last column of w is the current token's.  The inputs before a segment's first row come from the request's tail
 // (state [slots, taps - 1, C], the last taps - 1 inputs of the request, zero at its start), which the same call
 // moves on.  x and y are column slices [n, C] of wider float32 matrices.  A thread owns one channel of one chunk
 // of a segment's tokens; the threads of the first chunk read the old tail before they write the new one, and
@@ -499,7 +499,7 @@ HK_API int hk_mingru_scan(const float* proj, long long ld, const float* z_bias, 
 // taps - 1 before them stay in registers from the group before), then the group's outputs are summed, oldest tap first.
 __global__ void __launch_bounds__(128)
 short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w, const int* __restrict__ segs,
-                  float* __restrict__ tail, float* __restrict__ y, long long ldy, int C, int taps) {
+                  float* __restrict__ tail, float* __restrict__ y, long long ldy, int C, int taps, int act) {
   const int seg = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
@@ -534,7 +534,7 @@ short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __res
     }
 #pragma unroll
     for (int u = 0; u < SC_GROUP; ++u)
-      if (tg + u < t1) y[(size_t)(row0 + tg + u) * ldy + c] = acc[u] / (1.0f + expf(-acc[u]));
+      if (tg + u < t1) y[(size_t)(row0 + tg + u) * ldy + c] = act ? acc[u] / (1.0f + expf(-acc[u])) : acc[u];
     float next[SC_MAX_TAPS];
 #pragma unroll
     for (int s = 1; s < SC_MAX_TAPS; ++s) next[s] = s <= SC_GROUP ? nw[SC_GROUP - s] : hist[s - SC_GROUP];
@@ -553,11 +553,11 @@ short_conv_kernel(const float* __restrict__ x, long long ldx, const float* __res
 }
 
 HK_API int hk_short_conv(const float* x, long long ldx, const float* w, const int* segs, int n_seg, int n_rows, float* tail,
-                         float* y, long long ldy, int C, int taps, void* stream) {
+                         float* y, long long ldy, int C, int taps, int act, void* stream) {
   if (n_seg <= 0 || n_rows <= 0 || C <= 0) return 0;
-  if (taps < 1 || taps > SC_MAX_TAPS) return HK_ERR_UNSUPPORTED;
+  if (taps < 1 || taps > SC_MAX_TAPS || act < 0 || act > 1) return HK_ERR_UNSUPPORTED;
   dim3 grid((unsigned)n_seg, (unsigned)((C + 127) / 128), (unsigned)((n_rows + SC_TOKENS - 1) / SC_TOKENS));
-  return hk_launch(short_conv_kernel, grid, dim3(128), 0, (cudaStream_t)stream, x, ldx, w, segs, tail, y, ldy, C, taps);
+  return hk_launch(short_conv_kernel, grid, dim3(128), 0, (cudaStream_t)stream, x, ldx, w, segs, tail, y, ldy, C, taps, act);
 }
 
 // ------------------------------------------------------------------ gated delta rule
@@ -627,6 +627,72 @@ HK_API int hk_gated_delta_scan(const float* q, const float* k, const float* v, l
   const long long items = (long long)n_rows * H;
   int e = hk_launch(gated_delta_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, q, k, v, ld, bl, al, ldg, a_log,
                     dt_bias, rec, items, H, G, dk, dv, L, rpt, q_scale, unit_eps);
+  if (e) return e;
+  return dr_scan_records(rec, segs, n_seg, state, out, H, dk, dv, L, rpt, s);
+}
+
+// ------------------------------------------------------------------ retention
+// Linear attention with a fixed decay per head and neither softmax nor denominator:
+//     S <- decay_h S + k v^T;   o = S^T q
+// q and k [n, H * dk] are first turned by position on their first `rot` dims (dim i paired with i + rot / 2, angle from
+// the tables cos, sin [positions, rot / 2]; rot = 0: no rotation), k then times k_scale.  As a record of the generalised
+// rule it is (d, a*u, u, k, r, v) = (decay_h, 0, 0, k, q, v): the scan above runs it.
+__global__ void retention_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                      long long ld, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                                      const int* __restrict__ positions, const float* __restrict__ decay, float* __restrict__ rec,
+                                      long long items, int H, int dk, int dv, int L, int RPT, float k_scale) {
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const size_t row = (size_t)(item / H);
+  const int h = (int)(item % H);
+  const float* qp = q + row * ld + (size_t)h * dk;
+  const float* kp = k + row * ld + (size_t)h * dk;
+  const int half = rot >> 1;
+  const float* c = cos_t + (size_t)positions[row] * half;
+  const float* s = sin_t + (size_t)positions[row] * half;
+  const float dec = decay[h];
+  const int P = L * RPT;
+  float* out = rec + (size_t)item * (5 * P + dv);
+  for (int j = lane; j < P; j += 32) {
+    const int i = (j % RPT) * L + j / RPT;       // the entry that sits at place j
+    float d = 0.f, kv = 0.f, qv = 0.f;
+    if (i < dk) {
+      d = dec;
+      if (i < half) {
+        kv = kp[i] * c[i] - kp[i + half] * s[i];
+        qv = qp[i] * c[i] - qp[i + half] * s[i];
+      } else if (i < rot) {
+        kv = kp[i] * c[i - half] + kp[i - half] * s[i - half];
+        qv = qp[i] * c[i - half] + qp[i - half] * s[i - half];
+      } else {
+        kv = kp[i];
+        qv = qp[i];
+      }
+      kv *= k_scale;
+    }
+    out[j] = d;
+    out[P + j] = 0.f;
+    out[2 * P + j] = 0.f;
+    out[3 * P + j] = kv;
+    out[4 * P + j] = qv;
+  }
+  for (int cidx = lane; cidx < dv; cidx += 32) out[5 * P + cidx] = v[row * ld + (size_t)h * dv + cidx];
+}
+
+// q, k [n, H*dk] and v [n, H*dv] are column slices of one float32 matrix (row stride ld); decay float32 [H]; `rec` as for
+// hk_delta_rule_scan.
+HK_API int hk_retention_scan(const float* q, const float* k, const float* v, long long ld, const float* cos_t, const float* sin_t,
+                             int rot, const int* positions, const float* decay, const int* segs, int n_seg, int n_rows, float* rec,
+                             float* state, float* out, int H, int dk, int dv, float k_scale, void* stream) {
+  if (n_seg <= 0 || n_rows <= 0) return 0;
+  if (H < 1 || dk < 1 || dv < 1 || dk > 2048 || rot < 0 || rot > dk || (rot & 1) || ((uintptr_t)rec & 15)) return HK_ERR_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  int L, rpt;
+  if (!dr_plan(n_seg, H, dk, dv, &L, &rpt)) return HK_ERR_UNSUPPORTED;
+  const long long items = (long long)n_rows * H;
+  int e = hk_launch(retention_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, q, k, v, ld, cos_t, sin_t, rot,
+                    positions, decay, rec, items, H, dk, dv, L, rpt, k_scale);
   if (e) return e;
   return dr_scan_records(rec, segs, n_seg, state, out, H, dk, dv, L, rpt, s);
 }
@@ -747,8 +813,8 @@ HK_API int hk_mlstm_scan(const float* q, const float* k, const float* v, const f
 // One warp per (token, head): y = N(o / den) * weight * act(g), narrowed to T.  N divides by the root mean square over the
 // head's dv values (eps inside the root).  o is read from rows of `ldo` floats per head (dv of them used).  `den`:
 // with gates != null the head's values are first divided by max(|o[dv]|, gates[item, 2]) + den_eps (the mLSTM's
-// normaliser: o[dv] is n . q, gates[.., 2] is e^(-m)).  The weight is [H, dv], or [dv] shared by the heads; act is the
-// logistic function or silu.
+// normaliser: o[dv] is n . q, gates[.., 2] is e^(-m)).  The weight is [H, dv], or [dv] shared by the heads, or null (a
+// norm without a weight); act is the logistic function or silu.
 template <typename T>
 __global__ void head_out_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ g, long long ldg,
                                      const float* __restrict__ weight, int shared_weight, int act, const float* __restrict__ gates,
@@ -768,11 +834,11 @@ __global__ void head_out_gate_kernel(const float* __restrict__ o, int ldo, const
   }
   ss = warp_sum(ss);
   const float inv = scale / sqrtf(ss / (float)dv + eps);
-  const float* wp = weight + (shared_weight ? 0 : (size_t)h * dv);
+  const float* wp = weight == nullptr ? nullptr : weight + (shared_weight ? 0 : (size_t)h * dv);
   for (int i = lane; i < dv; i += 32) {
     const float gl = g[(size_t)t * ldg + (size_t)h * dv + i];
     const float gate = act == 0 ? sigmoid_f(gl) : gl * sigmoid_f(gl);
-    out[(size_t)item * dv + i] = from_f32<T>(src[i] * inv * wp[i] * gate);
+    out[(size_t)item * dv + i] = from_f32<T>(src[i] * inv * (wp ? wp[i] : 1.0f) * gate);
   }
 }
 

@@ -4,7 +4,13 @@
 // on its number of rows alone (a decode step through it can be captured in a graph):
 //   1. route:   one block per token takes the E router logits (float32 products of the token's vector with
 //               the router's rows, summed in a fixed order), picks the `top` largest (the lower index wins a
-//               tie) and gives them the softmax over the chosen logits as weights.
+//               tie) and gives them the softmax over the chosen logits as weights.  A second mode scores every
+//               expert by itself: s = sigmoid(logit); the choice is made on s + correction (a float per expert),
+//               optionally among the experts of the best `keep` of `groups` equal groups of neighbours (a
+//               group's score: the sum of its two largest choice scores), and the weights are the chosen
+//               experts' s over their sum (+ norm_eps), times a factor.  The router's matrix may carry further
+//               rows behind the experts' (`extra`): their logits' sigmoids are handed out per token (a gate
+//               of a sublayer that every token uses).
 //   2. sort:    one CTA counts the (token, choice) pairs per expert, lays the experts' rows out one after
 //               the other (`perm`: sorted place -> pair, `inv`: pair -> sorted place) and cuts every
 //               expert's rows into tiles of RT_BM rows (`tiles`: expert and first row, -1 for unused).
@@ -23,15 +29,28 @@
 
 // ------------------------------------------------------------------------------------ 1. route
 #define RK_WARPS 8
+struct RouteOpts {
+  int mode;                  // 0: softmax over the chosen logits; 1: sigmoid scores
+  const float* correction;   // mode 1: added to the scores for the choice alone (null: nothing)
+  int groups, keep;          // mode 1: the choice is made inside the best `keep` of `groups` groups (groups 0: everywhere)
+  float scale, norm_eps;     // mode 1: weights = s / (sum s + norm_eps) * scale
+  int extra;                 // rows of w behind the E experts' rows
+  float* extra_out;          // [n, extra]: the sigmoids of those rows' logits
+};
+
 template <typename T>
 __global__ void __launch_bounds__(RK_WARPS * 32)
 route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ weights, int n,
-                  int d, int E, int top) {
-  extern __shared__ float sm[];               // [RK_WARPS][E] partial logits, then [E] logits
+                  int d, int n_experts, int top, RouteOpts opt) {
+  extern __shared__ float sm[];               // [RK_WARPS][E] partial logits, then [E] logits, [n_experts] scores, [groups] x 2
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int t = blockIdx.x;                   // a block per token: its warps share the token's vector
+  int E = n_experts + opt.extra;              // rows of the router's matrix
   float* part = sm;
   float* z = sm + (size_t)RK_WARPS * E;
+  float* score = z + E;
+  float* gscore = score + n_experts;
+  float* gkept = gscore + opt.groups;
   const T* xr = x + (size_t)t * d;
   for (int e0 = 0; e0 < E; e0 += 8) {          // eight experts per pass over the token's vector
     float acc[8];
@@ -71,6 +90,59 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __r
   }
   __syncthreads();
   if (wid != 0) return;
+  E = n_experts;
+  if (opt.mode == 1) {
+    for (int e = lane; e < E; e += 32) {
+      const float sc = 1.0f / (1.0f + expf(-z[e]));
+      score[e] = sc;
+      z[e] = opt.correction != nullptr ? sc + opt.correction[e] : sc;
+    }
+    for (int e = lane; e < opt.extra; e += 32) opt.extra_out[(size_t)t * opt.extra + e] = 1.0f / (1.0f + expf(-z[E + e]));
+    __syncwarp();
+    if (opt.groups > 0 && opt.keep < opt.groups) {
+      const int size = E / opt.groups;
+      for (int g = lane; g < opt.groups; g += 32) {          // a group's score: its two largest choice scores
+        float a = -CUDART_INF_F, b = -CUDART_INF_F;
+        for (int e = g * size; e < (g + 1) * size; ++e) {
+          const float v = z[e];
+          if (v > a) {
+            b = a;
+            a = v;
+          } else if (v > b) {
+            b = v;
+          }
+        }
+        gscore[g] = size > 1 ? a + b : a;
+        gkept[g] = 0.f;
+      }
+      __syncwarp();
+      for (int k = 0; k < opt.keep; ++k) {                   // the best groups, the lower index winning a tie
+        float best = -CUDART_INF_F;
+        int bi = 0x7fffffff;
+        for (int g = lane; g < opt.groups; g += 32) {
+          const float v = gscore[g];
+          if (gkept[g] == 0.f && (v > best || bi == 0x7fffffff)) {
+            best = v;
+            bi = g;
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > best || (ov == best && oi < bi))) {
+            best = ov;
+            bi = oi;
+          }
+        }
+        if (lane == 0 && bi < opt.groups) gkept[bi] = 1.f;
+        __syncwarp();
+      }
+      for (int e = lane; e < E; e += 32)
+        if (gkept[e / size] == 0.f) z[e] = -CUDART_INF_F;
+      __syncwarp();
+    }
+  }
   float first = 0.f, mine = 0.f, total = 0.f;
   int mine_id = 0;
   for (int k = 0; k < top; ++k) {
@@ -93,7 +165,8 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __r
       }
     }
     if (k == 0) first = best;
-    const float p = expf(best - first);        // the first chosen logit is the largest
+    // mode 0: the first chosen logit is the largest; mode 1: the expert's own score, without the correction
+    const float p = opt.mode == 1 ? (bi < E ? score[bi] : 0.f) : expf(best - first);
     total += p;
     if (lane == (k & 31)) {                    // lane k keeps choice k (top <= 32)
       mine = p;
@@ -104,26 +177,30 @@ route_topk_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __r
   }
   if (lane < top) {
     ids[(size_t)t * top + lane] = mine_id < E ? mine_id : 0;
-    weights[(size_t)t * top + lane] = mine / total;
+    weights[(size_t)t * top + lane] = opt.mode == 1 ? mine / (total + opt.norm_eps) * opt.scale : mine / total;
   }
 }
 
-HK_API int hk_route_topk(const void* x, int dtype, const float* w, int* ids, float* weights, int n, int d, int E, int top,
+HK_API int hk_route_topk(const void* x, int dtype, const float* w, int* ids, float* weights, int n, int d, int E, int top, int mode,
+                         const float* correction, int groups, int keep, float scale, float norm_eps, int extra, float* extra_out,
                          void* stream) {
   if (n <= 0) return 0;
-  if (E < 1 || top < 1 || top > E || top > 32 || E > 2048) return HK_ERR_UNSUPPORTED;
-  const size_t smem = (size_t)(RK_WARPS + 1) * E * sizeof(float);
+  if (E < 1 || top < 1 || top > E || top > 32 || E > 2048 || mode < 0 || mode > 1 || extra < 0 || extra > 64) return HK_ERR_UNSUPPORTED;
+  if (mode == 0 && (correction != nullptr || groups != 0 || extra != 0)) return HK_ERR_UNSUPPORTED;
+  if (groups < 0 || (groups > 0 && (E % groups || keep < 1 || keep > groups)) || (extra > 0 && extra_out == nullptr)) return HK_ERR_UNSUPPORTED;
+  const RouteOpts opt = {mode, correction, groups, keep, scale, norm_eps, extra, extra_out};
+  const size_t smem = ((size_t)(RK_WARPS + 1) * (E + extra) + E + 2 * groups) * sizeof(float);
   dim3 grid((unsigned)n);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == HK_F32) {
     static HkSmemCache cache;
     if (int e = hk_allow_smem(route_topk_kernel<float>, smem, cache)) return e;
-    return hk_launch(route_topk_kernel<float>, grid, dim3(RK_WARPS * 32), smem, s, (const float*)x, w, ids, weights, n, d, E, top);
+    return hk_launch(route_topk_kernel<float>, grid, dim3(RK_WARPS * 32), smem, s, (const float*)x, w, ids, weights, n, d, E, top, opt);
   }
   if (dtype == HK_BF16) {
     static HkSmemCache cache;
     if (int e = hk_allow_smem(route_topk_kernel<bf16>, smem, cache)) return e;
-    return hk_launch(route_topk_kernel<bf16>, grid, dim3(RK_WARPS * 32), smem, s, (const bf16*)x, w, ids, weights, n, d, E, top);
+    return hk_launch(route_topk_kernel<bf16>, grid, dim3(RK_WARPS * 32), smem, s, (const bf16*)x, w, ids, weights, n, d, E, top, opt);
   }
   return HK_ERR_UNSUPPORTED;
 }
@@ -496,21 +573,25 @@ HK_API int hk_grouped_gemm(const void* a, const void* w, int dtype, void* out, c
 }
 
 // ------------------------------------------------------------------------------------ 4. combine
-// y[t, :] (= or +=) sum_k weights[t, k] * ys[inv[t * top + k], :]
+// y[t, :] (= or +=) sum_k weights[t, k] * ys[inv[t * top + k], :] (+ shared_gate[t] * shared[t, :], the result of a
+// sublayer that every token uses, when `shared` is given; a null gate counts as 1)
 __global__ void route_combine_kernel(const float* __restrict__ ys, const int* __restrict__ inv, const float* __restrict__ weights,
-                                     float* __restrict__ y, int d, int top, int accumulate) {
+                                     float* __restrict__ y, int d, int top, int accumulate, const float* __restrict__ shared,
+                                     const float* __restrict__ shared_gate) {
   const int t = blockIdx.x;
+  const float sg = shared != nullptr ? (shared_gate != nullptr ? shared_gate[t] : 1.0f) : 0.f;
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(weights[(size_t)t * top + k], ys[(size_t)inv[(size_t)t * top + k] * d + i], acc);
+    if (shared != nullptr) acc = fmaf(sg, shared[(size_t)t * d + i], acc);
     float* o = y + (size_t)t * d + i;
     *o = accumulate ? *o + acc : acc;
   }
 }
 
 HK_API int hk_route_combine(const float* ys, const int* inv, const float* weights, float* y, int n, int d, int top, int accumulate,
-                            void* stream) {
+                            const float* shared, const float* shared_gate, void* stream) {
   if (n <= 0) return 0;
   return hk_launch(route_combine_kernel, dim3((unsigned)n), dim3(d >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, ys, inv, weights,
-                   y, d, top, accumulate);
+                   y, d, top, accumulate, shared, shared_gate);
 }

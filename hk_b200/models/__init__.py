@@ -1,4 +1,4 @@
-from . import kedanex, mifolorn, padodra, qwen3  # noqa: F401  (register the architectures)
+from . import kedanex, mifolorn, padodra, qwen3, zazulix  # noqa: F401  (register the architectures)
 from .spec import LayerCall, ModelSpec
 
 __all__ = ["LayerCall", "ModelSpec"]

@@ -1,4 +1,4 @@
-from .attention import GQAAttention
+from .attention import DifferentialAttention, GQAAttention
 from .base import (KVCacheSpec, MATRIX, ParamSpec, Part, Precision, StateSpec, StepTables, TABLE, VECTOR, part_class,
                    register_part)
 from .block import PostNormBlock, PreNormBlock, SandwichNormBlock
@@ -8,11 +8,11 @@ from .latent_attention import LatentAttention
 from .norm import RMSNorm
 from .parallel import ParallelMixer
 from .position import RopeScaling, RotaryEmbedding
-from .recurrent import GatedDeltaRule, GeneralDeltaRule, MLSTM, MinGRU
+from .recurrent import GatedDeltaRule, GeneralDeltaRule, MLSTM, MinGRU, Retention, ShortConvolution
 from .side_input import TokenSideInput
 
 __all__ = [
-    "GQAAttention", "GatedDeltaRule", "GeneralDeltaRule", "MLSTM", "ParallelMixer", "TokenSideInput", "KVCacheSpec", "LatentAttention", "MinGRU", "PostNormBlock", "PolyNormFeedForward", "RoutedFeedForward", "SandwichNormBlock", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
+    "DifferentialAttention", "GQAAttention", "GatedDeltaRule", "Retention", "ShortConvolution", "GeneralDeltaRule", "MLSTM", "ParallelMixer", "TokenSideInput", "KVCacheSpec", "LatentAttention", "MinGRU", "PostNormBlock", "PolyNormFeedForward", "RoutedFeedForward", "SandwichNormBlock", "MATRIX", "OutputHead", "ParamSpec", "Part", "Precision", "PreNormBlock",
     "RMSNorm", "RopeScaling", "RotaryEmbedding", "StateSpec", "StepTables", "SwiGLUFeedForward", "TABLE", "TokenEmbedding", "VECTOR",
     "part_class", "register_part",
 ]

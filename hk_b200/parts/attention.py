@@ -246,3 +246,129 @@ class GQAAttention(Part):
 
 
 register_part("mixer", "gqa_attention", GQAAttention)
+
+
+class DifferentialAttention(Part):
+    """Grouped-query attention with two score maps per head over the same values ("differential attention").
+
+        q = W_q h [H, 2, dim],  k = W_k h [G, 2, dim],  v = W_v h [G, vdim]      a head's two maps side by side
+        optionally a short causal convolution per channel of q, k and v (`taps`), straight behind the projections
+        rotation of the first `position.rotary_dim` dims of every map of q and k
+        a_j = softmax(scale * q_j k_j^T) v  for j = 1, 2     (causal; `window` limits the keys)
+        lambda = exp(sum(lq1 * lk1)) - exp(sum(lq2 * lk2)) + diff                one number for the mixer
+        o = a_1 - lambda * a_2;   o <- o / sqrt(mean(o^2) + norm_eps) * (1 - diff)   per head, no weight
+        y = W_o (o * sigmoid(W_g h)_head)                                        `gate`: one number per head
+
+    It runs on the ordinary paged attention kernels as 2 H query heads over G key/value heads: the cache row of a key
+    head holds both maps' keys side by side, and a map's query is zero outside its own half, so both maps of all heads
+    of a group read the same keys and values once.  Where the cache rows have a head size the tensor-core kernels know
+    (2 dim = vdim), those run; else the generic kernel.  The cache is `KVCacheSpec(G, 2 dim, window, vdim)` and, with a
+    convolution, its last taps - 1 inputs per request.  `names` renames the tensors (keys q, k, v, o, gate, q_conv, k_conv,
+    v_conv, lq1, lk1, lq2, lk2)."""
+    graph_safe = True   # reads the batch from device tensors only
+    MAPS = 2
+
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int, prefix: str, diff: float,
+                 norm_eps: float, scale: Optional[float] = None, position: Optional[RotaryEmbedding] = None,
+                 window: Optional[int] = None, taps: int = 0, gate: bool = True, names: Optional[Dict[str, str]] = None):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
+        if position is not None and (position.rotary_dim > head_dim or position.pairing != "half"):
+            raise ValueError("the rotation must fit a map's size and pair dim i with i + dims/2")
+        if self.MAPS * head_dim > 640 or v_head_dim > 640 or min(head_dim, v_head_dim) < 1:
+            raise ValueError("a cache row of a differential attention holds at most 640 numbers")
+        self.hidden, self.H, self.G, self.dk, self.vd = hidden, n_heads, n_kv_heads, head_dim, v_head_dim
+        self.prefix, self.diff, self.norm_eps = prefix, float(diff), float(norm_eps)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.position, self.window, self.gate = position, window, bool(gate)
+        self.names = {"q": "q", "k": "k", "v": "v", "o": "o", "gate": "g", "q_conv": "q.conv", "k_conv": "k.conv",
+                      "v_conv": "v.conv", "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
+        self.names.update(names or {})
+        M = self.MAPS
+        self.channels = (n_heads + n_kv_heads) * M * head_dim + n_kv_heads * v_head_dim
+        self.conv = None
+        if taps:
+            from .recurrent import ShortConvolution
+            nm = self.names
+            self.conv = ShortConvolution([(prefix + nm["q_conv"], n_heads * M * head_dim), (prefix + nm["k_conv"], n_kv_heads * M * head_dim),
+                                          (prefix + nm["v_conv"], n_kv_heads * v_head_dim)], taps, act="none")
+        self.w_in = self.w_o = None
+        self.lam = 0.0
+        self._tables_key = None
+        self._sm_count = 0
+
+    def _flash_takes(self) -> bool:
+        from ..csrc import attention_fast
+        return self.vd == self.MAPS * self.dk and attention_fast.supported(self.vd, self.MAPS * self.H // self.G)
+
+    def kernel_libraries(self, bfloat16: bool):
+        from ..csrc import attention_fast
+        if not bfloat16 or not self._flash_takes():
+            return ()
+        return ("attention_flash", "attention_prefill_tc") if attention_fast.tc_prefill_supported(self.vd, self.MAPS * self.H // self.G) \
+            else ("attention_flash",)
+
+    def children(self):
+        return tuple(p for p in (self.position, self.conv) if p is not None)
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        p, nm, H, G, dk, vd, d, M = self.prefix, self.names, self.H, self.G, self.dk, self.vd, self.hidden, self.MAPS
+        specs = {p + nm["q"]: ParamSpec((H * M * dk, d), MATRIX), p + nm["k"]: ParamSpec((G * M * dk, d), MATRIX),
+                 p + nm["v"]: ParamSpec((G * vd, d), MATRIX), p + nm["o"]: ParamSpec((d, H * vd), MATRIX)}
+        for key in ("lq1", "lk1", "lq2", "lk2"):
+            specs[p + nm[key]] = ParamSpec((dk,), VECTOR)
+        if self.gate:
+            specs[p + nm["gate"]] = ParamSpec((H, d), MATRIX)
+        return specs
+
+    def cache_specs(self):
+        pages = KVCacheSpec(self.G, self.MAPS * self.dk, self.window, self.vd)
+        return [pages, self.conv.cache_spec()] if self.conv is not None else [pages]
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        p, nm = self.prefix, self.names
+        mats = [tensors[p + nm[c]] for c in ("q", "k", "v")] + ([tensors[p + nm["gate"]]] if self.gate else [])
+        wide = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.w_in = torch.cat([t.to(wide) for t in mats], dim=0).contiguous()     # one product: q, k, v and the heads' gates
+        self.w_o = tensors[p + nm["o"]]
+        l = [tensors[p + nm[key]].float() for key in ("lq1", "lk1", "lq2", "lk2")]
+        # lambda in 32-bit, once: it is the same for every token
+        self.lam = float((torch.exp((l[0] * l[1]).sum()) - torch.exp((l[2] * l[3]).sum()) + self.diff).item())
+        if precision.compute == torch.bfloat16 and self._flash_takes():
+            self._tables_key = ("paged_attention_items", self.window or 0, self.MAPS * self.H, self.G, self.vd, False, 0, False)
+            self._sm_count = torch.cuda.get_device_properties(precision.device).multi_processor_count
+
+    def step_tables_key(self):
+        return self._tables_key
+
+    def step_tables(self, ctx):
+        return flash_step_tables(ctx, self.MAPS * self.H, self.G, self.vd, self.window or 0, 0, self._sm_count)
+
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
+                accumulate: bool = True) -> None:
+        n, dev, dt = xb.shape[0], xb.device, xb.dtype
+        H, G, dk, vd, M, C = self.H, self.G, self.dk, self.vd, self.MAPS, self.channels
+        pages = cache[0]
+        proj = torch.empty((n, self.w_in.shape[0]), dtype=torch.float32, device=dev)
+        ops.gemm(xb, self.w_in, proj)
+        x = proj[:, :C]
+        if self.conv is not None:
+            x = torch.empty((n, C), dtype=torch.float32, device=dev)
+            self.conv.forward(proj[:, :C], ctx, cache[1], x)
+        cos = sin = None
+        rot = 0
+        if self.position is not None:
+            cos, sin, rot = self.position.tables()
+        q = torch.empty((n, H * M * M * dk), dtype=dt, device=dev)
+        ops.maps_rope_kv_write(x, q, cos, sin, rot, ctx.positions, ctx.slot_of_token, pages.block_table, pages.k_pages,
+                               pages.v_pages, H, G, M, dk, pages.page_tokens, write_kv=write_cache)
+        plan = flash_plan(ctx, self._tables_key) if dt == torch.bfloat16 else None
+        att = torch.empty((n, M * H * vd), dtype=dt, device=dev)
+        ops.paged_attention(q, pages.k_pages, pages.v_pages, pages.block_table, ctx.positions, ctx.slot_of_token, att,
+                            M * H, G, M * dk, pages.page_tokens, self.window or 0, self.scale, plan=plan)
+        og = torch.empty((n, H * vd), dtype=dt, device=dev)
+        ops.diff_heads_out(att, proj[:, C:C + H] if self.gate else None, og, H, vd, self.lam, self.norm_eps, 1.0 - self.diff)
+        ops.gemm(og, self.w_o, residual, accumulate=accumulate)
+
+
+register_part("mixer", "differential_attention", DifferentialAttention)

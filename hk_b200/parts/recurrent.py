@@ -36,6 +36,17 @@ output is float32.
       y = W_o ((o / rms(o) per head) * norm_weight[n_heads * value_dim] * sigmoid(W_g h))
   n is kept as one more column of S (its value is always 1), m in a `StateSpec` of its own.
 
+`Retention` (per head a matrix state S [key_dim, value_dim], zero at the start; a fixed decay per head, no softmax and no
+denominator):
+      q, k = rot(W_q h), rot(W_k h) * k_scale;   v = W_v h          rot: the position encoding handed in (or none)
+      S <- decay_h S + k v^T;   o = S^T q
+      y = W_o ((o / rms(o) per head) * silu(W_g h))
+  `decay` (one number per head) and `k_scale` (key_dim^(-1/2) by default) are parameters.
+
+`ShortConvolution` is the causal convolution over a request's last `taps` rows per channel as a part of its own (tensors
+[channels, taps] by group of channels, an optional silu, the request's last taps - 1 inputs as its state), for mixers
+other than the gated delta rule that put one behind their projections.
+
 A mixer with several caches says so with `cache_specs()` and is handed the list.
 """
 from __future__ import annotations
@@ -243,6 +254,86 @@ class GatedDeltaRule(_SegmentScan):
         ops.gemm(og, self.w_o, residual, accumulate=accumulate)
 
 
+class Retention(_SegmentScan):
+    def __init__(self, hidden: int, n_heads: int, key_dim: int, value_dim: int, decay, prefix: str, norm_eps: float,
+                 position=None, k_scale: Optional[float] = None, names: Optional[Dict[str, str]] = None):
+        decay = [float(x) for x in decay]
+        if len(decay) != n_heads:
+            raise ValueError(f"{len(decay)} decays for {n_heads} heads")
+        if position is not None and (position.rotary_dim > key_dim or position.pairing != "half"):
+            raise ValueError("the rotation must fit the key size and pair dim i with i + dims/2")
+        self.hidden, self.H, self.dk, self.dv = hidden, n_heads, key_dim, value_dim
+        self.decay_values, self.prefix, self.norm_eps, self.position = decay, prefix, float(norm_eps), position
+        self.k_scale = float(k_scale) if k_scale is not None else key_dim ** -0.5
+        self.names = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+        self.names.update(names or {})
+        self.w_in = self.w_o = self.decay = None
+
+    def children(self):
+        return (self.position,) if self.position is not None else ()
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        p, nm, d = self.prefix, self.names, self.hidden
+        K, V = self.H * self.dk, self.H * self.dv
+        return {p + nm["q"]: ParamSpec((K, d), MATRIX), p + nm["k"]: ParamSpec((K, d), MATRIX),
+                p + nm["v"]: ParamSpec((V, d), MATRIX), p + nm["g"]: ParamSpec((V, d), MATRIX),
+                p + nm["o"]: ParamSpec((d, V), MATRIX)}
+
+    def cache_spec(self):
+        return StateSpec((self.H, self.dk, self.dv), torch.float32)
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        p, nm = self.prefix, self.names
+        mats = [tensors[p + nm[c]] for c in ("q", "k", "v", "g")]
+        wide = torch.float32 if any(t.dtype == torch.float32 for t in mats) else mats[0].dtype
+        self.w_in = torch.cat([t.to(wide) for t in mats], dim=0).contiguous()
+        self.w_o = tensors[p + nm["o"]]
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).to(precision.device)
+
+    def forward(self, xb: torch.Tensor, residual: torch.Tensor, ctx, cache, write_cache: bool = True,
+                accumulate: bool = True) -> None:
+        n = xb.shape[0]
+        K, V = self.H * self.dk, self.H * self.dv
+        proj = torch.empty((n, self.w_in.shape[0]), dtype=torch.float32, device=xb.device)
+        ops.gemm(xb, self.w_in, proj)
+        cos = sin = None
+        rot = 0
+        if self.position is not None:
+            cos, sin, rot = self.position.tables()
+        o = torch.empty((n, V), dtype=torch.float32, device=xb.device)
+        ops.retention_scan(proj[:, :K], proj[:, K:2 * K], proj[:, 2 * K:2 * K + V], cos, sin, rot, ctx.positions, self.decay,
+                           self._segments(ctx), cache.state, o, self.H, self.dk, self.dv, self.k_scale)
+        og = torch.empty((n, V), dtype=xb.dtype, device=xb.device)
+        ops.head_out_gate(o, proj[:, 2 * K + V:], None, self.norm_eps, og, self.H, self.dv, act="silu")
+        ops.gemm(og, self.w_o, residual, accumulate=accumulate)
+
+
+class ShortConvolution(_SegmentScan):
+    """y[t, c] = act(sum_j w[c, j] x[t - (taps - 1) + j, c]) over a request's rows, zeros before its start.  `groups`:
+    (tensor name, channels) in the order of the channels; the tensors [channels, taps] are laid side by side at binding."""
+
+    def __init__(self, groups, taps: int, act: str = "none"):
+        if taps < 1 or act not in ("none", "silu"):
+            raise ValueError("the short convolution needs at least one tap, and act 'none' or 'silu'")
+        self.groups, self.taps, self.act = [(str(nm), int(c)) for nm, c in groups], int(taps), act
+        self.channels = sum(c for _, c in self.groups)
+        self.weight = None
+
+    def own_param_specs(self) -> Dict[str, ParamSpec]:
+        return {nm: ParamSpec((c, self.taps), VECTOR) for nm, c in self.groups}
+
+    def cache_spec(self):
+        # one tap keeps no inputs; its tail is a row that nobody reads (a state of no size has no slot to live in)
+        return StateSpec((max(self.taps - 1, 1), self.channels), torch.float32)
+
+    def own_bind(self, tensors, precision: Precision) -> None:
+        self.weight = torch.cat([tensors[nm] for nm, _ in self.groups], dim=0).contiguous()
+
+    def forward(self, x: torch.Tensor, ctx, cache, out: torch.Tensor) -> None:
+        """x and out: float32 column slices [n, channels]; `cache`: the state of `cache_spec()`."""
+        ops.short_conv(x, self.weight, self._segments(ctx), cache.state, out, act=self.act)
+
+
 class MLSTM(_SegmentScan):
     def __init__(self, hidden: int, n_heads: int, key_dim: int, value_dim: int, gate_cap: float, prefix: str, norm_eps: float,
                  den_eps: float = 1e-6, q_scale: Optional[float] = None, names: Optional[Dict[str, str]] = None):
@@ -301,3 +392,4 @@ register_part("mixer", "general_delta_rule", GeneralDeltaRule)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)
 register_part("mixer", "mlstm", MLSTM)
 register_part("mixer", "mingru", MinGRU)
+register_part("mixer", "retention", Retention)
