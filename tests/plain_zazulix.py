@@ -162,11 +162,13 @@ def expert(h, w, p):
 
 def route(z, correction, top, groups):
     """z [E] router logits of one token.  Returns (chosen experts in order of choice, their weights before the
-    router's factor, the gap between the last chosen and the best refused choice score)."""
+    router's factor, the smallest gap by which a choice was made: last kept against first refused group score, last
+    chosen against best refused choice score)."""
     s = sigmoid(z)
     choice = s + correction
     E = len(z)
     allowed = np.ones(E, dtype=bool)
+    margin = np.inf
     if groups:
         count, keep = int(groups["count"]), int(groups["keep"])
         size = E // count
@@ -175,10 +177,13 @@ def route(z, correction, top, groups):
         allowed[:] = False
         for g in order[:keep]:
             allowed[g * size:(g + 1) * size] = True
+        if keep < count:
+            margin = score[order[keep - 1]] - score[order[keep]]
     masked = np.where(allowed, choice, -np.inf)
     order = sorted(range(E), key=lambda e: (-masked[e], e))
     chosen = order[:top]
-    margin = masked[chosen[-1]] - masked[order[top]] if top < E else np.inf
+    if top < E:
+        margin = min(margin, masked[chosen[-1]] - masked[order[top]])
     weights = s[chosen] / (s[chosen].sum() + 1e-20)
     return chosen, weights, margin
 
