@@ -311,7 +311,7 @@ def main():
     ap.add_argument("--prefill-reps", type=int, default=7)
     ap.add_argument("--quick", action="store_true", help="skip batch 64")
     ap.add_argument("--design", default="", help="instead of the default workload: prefill and decode throughput of another "
-                    "model design (kedanex, padodra, mifolorn) beside the closest other decoder at equal width and depth, and its kernels one by one")
+                    "model design (kedanex, padodra, mifolorn, zazulix) beside the closest other decoder at equal width and depth, and its kernels one by one")
     ap.add_argument("--design-widths", default="2048,4096", help="model widths for --design, with commas between them")
     args = ap.parse_args()
     if args.impl == "reference":

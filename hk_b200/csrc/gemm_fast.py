@@ -159,8 +159,9 @@ def stream_wanted(M: int, N: int, K: int) -> bool:
     return (M <= STREAM_M_AUTO and N * K >= STREAM_MIN_WEIGHTS) or STREAM_M_AUTO < M <= STREAM_M_AUTO_WIDE
 
 
-def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
-    """The persistent streaming kernel; epilogue 0 store, 1 add, 2 silu(gate) * up (3: tanh gelu) over w = [gate rows | up rows]."""
+def run_stream(a, w, out, epilogue: int, ldo: int, limit: float = 0.0, slope: float = 1.0) -> bool:
+    """The persistent streaming kernel; epilogue 0 store, 1 add, 2 silu(gate) * up (3: tanh gelu; 4: the clamped form with
+    its limit and slope) over w = [gate rows | up rows]."""
     from . import ops
     M, K = a.shape
     N = w.shape[0]
@@ -171,9 +172,14 @@ def run_stream(a, w, out, epilogue: int, ldo: int) -> bool:
     if scratch is None:
         return False
     ws, ct = scratch
-    code = lib.hk_gemm_stream(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(ldo), epilogue,
-                              stream_row_warps(N, _sms(a.device)),
-                              _ptr(ws), _ptr(ct), _ptr(status_flag(a.device)), _stream_ctas, _stream())
+    if epilogue == 4:
+        code = lib.hk_gemm_stream_clamped(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(ldo),
+                                          stream_row_warps(N, _sms(a.device)), _ptr(ws), _ptr(ct), _ptr(status_flag(a.device)),
+                                          _stream_ctas, ctypes.c_float(limit), ctypes.c_float(slope), _stream())
+    else:
+        code = lib.hk_gemm_stream(_ptr(a), _ptr(w), _ptr(out), M, N, K, ctypes.c_longlong(ldo), epilogue,
+                                  stream_row_warps(N, _sms(a.device)),
+                                  _ptr(ws), _ptr(ct), _ptr(status_flag(a.device)), _stream_ctas, _stream())
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "gemm (streaming)")
@@ -223,9 +229,9 @@ def run(a, w, out, accumulate: bool, choice: Optional[str]) -> bool:
 
 def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None, act: int = 0, limit: float = 0.0, slope: float = 1.0) -> bool:
     """out (bf16 [M, F]) = act(gate) * up of a w^T for w = [F gate rows | F up rows], in the epilogue of the
-    streaming kernel (few rows) or of the tcgen05 kernel; act 0 is silu, 1 the tanh form of gelu.  False when they
-    refuse (the clamped form, act 2, is not fused: the caller runs the product and the activation kernel)."""
-    if act not in (0, 1):
+    streaming kernel (few rows) or of the tcgen05 kernel; act 0 is silu, 1 the tanh form of gelu, 2 the clamped form
+    g sigmoid(slope g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).  False when they refuse."""
+    if act not in (0, 1, 2):
         return False
     epilogue = 2 + int(act)
     from . import ops
@@ -234,7 +240,7 @@ def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None, act: int = 0, li
     if not _aligned(a, w_gate_up) or N % 2:
         return False
     if choice == "stream" or (choice is None and stream_wanted(M, N, K)):
-        if N % (16 * stream_row_warps(N, _sms(a.device))) == 0 and run_stream(a, w_gate_up, out, epilogue, out.shape[1]):
+        if N % (16 * stream_row_warps(N, _sms(a.device))) == 0 and run_stream(a, w_gate_up, out, epilogue, out.shape[1], limit, slope):
             return True
         if choice == "stream":
             return False
@@ -243,8 +249,13 @@ def run_swiglu(a, w_gate_up, out, choice: Optional[str] = None, act: int = 0, li
     lib = build.load("gemm_tc")
     bn, splits = tc_config(M, N, K, _sms(a.device), swiglu=True)
     partial = _tc_partial(lib, M, N, splits, a.device)
-    code = lib.hk_gemm_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), epilogue, bn,
-                          splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
+    if epilogue == 4:
+        code = lib.hk_gemm_tc_clamped(_ptr(a), _ptr(w_gate_up), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), bn, splits,
+                                      _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)),
+                                      ctypes.c_float(limit), ctypes.c_float(slope), _stream())
+    else:
+        code = lib.hk_gemm_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), M, N, K, ctypes.c_longlong(out.shape[1]), epilogue, bn,
+                              splits, _ptr(partial) if splits > 1 else ctypes.c_void_p(0), _ptr(status_flag(a.device)), _stream())
     if code == _UNSUPPORTED:
         return False
     ops._check(code, "gemm+swiglu (tcgen05)")

@@ -48,14 +48,23 @@ constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr int SMEM_BUDGET = 152 * 1024;
 constexpr int SMEM_BUDGET_WIDE = 200 * 1024;     // 17 to 32 rows: a stage is 48 KB, and three must fit
 
-enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GEGLU = 3 };
-// The two gated epilogues differ in the gate's activation alone: silu, or the tanh form of gelu, which is
-// g * sigmoid(2 * sqrt(2 / pi) * (g + 0.044715 g^3)).
-#define IS_GLU(e) ((e) == EPI_SWIGLU || (e) == EPI_GEGLU)
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GEGLU = 3, EPI_CLAMPGLU = 4 };
+// The first two gated epilogues differ in the gate's activation alone: silu, or the tanh form of gelu, which is
+// g * sigmoid(2 * sqrt(2 / pi) * (g + 0.044715 g^3)).  The third clamps both halves first: with g = min(gate, limit) and
+// u = clamp(up, -limit, limit) it gives g * sigmoid(slope * g) * (u + 1); limit and slope travel as kernel arguments.
+#define IS_GLU(e) ((e) == EPI_SWIGLU || (e) == EPI_GEGLU || (e) == EPI_CLAMPGLU)
+struct GluParams {
+  float limit, slope;
+};
 template <int EPI>
-__device__ __forceinline__ float glu_gate(float g) {
+__device__ __forceinline__ float glu_pair(float g, float u, GluParams gp) {
+  if (EPI == EPI_CLAMPGLU) {
+    g = fminf(g, gp.limit);
+    u = fminf(fmaxf(u, -gp.limit), gp.limit) + 1.0f;
+    return g / (1.0f + __expf(-gp.slope * g)) * u;
+  }
   const float z = EPI == EPI_GEGLU ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
-  return g / (1.0f + __expf(-z));
+  return g / (1.0f + __expf(-z)) * u;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -175,7 +184,7 @@ __device__ __forceinline__ Sched make_sched(int n_tiles, int kc, long long P, lo
 template <int RW, int MT, int EPI>
 __device__ __forceinline__ void consume_units(const Sched& sc, uint32_t i_base, uint32_t ring, Control* ctl, float* tile_buf,
                                               void* __restrict__ out, int M, int N, long long ldo, float* __restrict__ workspace,
-                                              int* __restrict__ counters) {
+                                              int* __restrict__ counters, GluParams gp) {
   using S = Shape<RW, MT>;
   constexpr int BN = S::BN, KW = S::KW, COLS = S::COLS, STAGES = S::STAGES;
   volatile int* abort_flag = &ctl->abort_flag;
@@ -259,7 +268,7 @@ __device__ __forceinline__ void consume_units(const Sched& sc, uint32_t i_base, 
             const int m = e / (BN / 2), row = e % (BN / 2);
             if (m >= M) continue;
             const float gate = value(m * BN + row), up = value(m * BN + row + BN / 2);
-            reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f0 + row] = __float2bfloat16_rn(glu_gate<EPI>(gate) * up);
+            reinterpret_cast<bf16*>(out)[(size_t)m * ldo + f0 + row] = __float2bfloat16_rn(glu_pair<EPI>(gate, up, gp));
           }
         } else {
           const int n0 = tile * BN;
@@ -330,7 +339,7 @@ template <int RW, int MT, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                    void* __restrict__ out, int M, int N, int K, long long ldo, float* __restrict__ workspace,
-                   int* __restrict__ counters, int* __restrict__ status) {
+                   int* __restrict__ counters, int* __restrict__ status, GluParams gp) {
   using S = Shape<RW, MT>;
   constexpr int BN = S::BN, BK = S::BK, KW = S::KW, STAGES = S::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -384,7 +393,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
     }
   } else {
-    consume_units<RW, MT, EPI>(sc, 0u, ring, ctl, tile_buf, out, M, N, ldo, workspace, counters);
+    consume_units<RW, MT, EPI>(sc, 0u, ring, ctl, tile_buf, out, M, N, ldo, workspace, counters, gp);
   }
   __syncthreads();
   if (threadIdx.x == 0 && ctl->abort_flag) atomicExch(status, 1);
@@ -434,7 +443,7 @@ int sm_count() {
 
 template <int RW, int MT, int EPI>
 int launch(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, float* workspace, int* counters,
-           int* status, int max_ctas, cudaStream_t s) {
+           int* status, int max_ctas, cudaStream_t s, GluParams gp = {0.f, 1.f}) {
   using S = Shape<RW, MT>;
   CUtensorMap ma, mw;
   if (!make_map(&ma, a, M, K, 8 * MT, S::KW) || !make_map(&mw, w, N, K, S::BN / 2, S::KW)) return HK_ERR_UNSUPPORTED;
@@ -446,15 +455,16 @@ int launch(const void* a, const void* w, void* out, int M, int N, int K, long lo
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (units < grid) grid = units;
   return hk_launch_pdl(gemm_stream_kernel<RW, MT, EPI>, dim3((unsigned)grid), dim3(NUM_THREADS), (size_t)S::SMEM, s, ma, mw, out, M, N, K,
-                   ldo, workspace, counters, status);
+                   ldo, workspace, counters, status, gp);
 }
 
 template <int RW, int MT>
 int launch_epi(int epilogue, const void* a, const void* w, void* out, int M, int N, int K, long long ldo, float* workspace,
-               int* counters, int* status, int max_ctas, cudaStream_t s) {
+               int* counters, int* status, int max_ctas, cudaStream_t s, GluParams gp) {
   if (epilogue == EPI_STORE) return launch<RW, MT, EPI_STORE>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
   if (epilogue == EPI_ADD) return launch<RW, MT, EPI_ADD>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
   if (epilogue == EPI_GEGLU) return launch<RW, MT, EPI_GEGLU>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
+  if (epilogue == EPI_CLAMPGLU) return launch<RW, MT, EPI_CLAMPGLU>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s, gp);
   return launch<RW, MT, EPI_SWIGLU>(a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
 }
 
@@ -468,21 +478,36 @@ int launch_epi(int epilogue, const void* a, const void* w, void* out, int M, int
 // before the first launch (left zero); status: device int that a timed-out wait sets to 1.
 // max_ctas: 0 = one CTA per SM; smaller values only for tests of the hand-over between CTAs.
 // Refuses (HK_ERR_UNSUPPORTED) M > 32, K % 64 != 0, operands not 16-byte aligned, bad rw.
-HK_API int hk_gemm_stream(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int rw,
-                          float* workspace, int* counters, int* status, int max_ctas, void* stream) {
+static int gemm_stream_run(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int rw,
+                           float* workspace, int* counters, int* status, int max_ctas, GluParams gp, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 32 || K <= 0 || (K & 63) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue < 0 || epilogue > 3 || (IS_GLU(epilogue) && (rw < 1 || N % (16 * rw)))) return HK_ERR_UNSUPPORTED;
+  if (epilogue < 0 || epilogue > 4 || (IS_GLU(epilogue) && (rw < 1 || N % (16 * rw)))) return HK_ERR_UNSUPPORTED;
   if (workspace == nullptr || counters == nullptr || status == nullptr) return HK_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
   const int mt = M <= 8 ? 1 : M <= 16 ? 2 : 4;
 #define HK_CASE(RW, MT) \
-  if (rw == RW && mt == MT) return launch_epi<RW, MT>(epilogue, a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s);
+  if (rw == RW && mt == MT) return launch_epi<RW, MT>(epilogue, a, w, out, M, N, K, ldo, workspace, counters, status, max_ctas, s, gp);
   HK_CASE(8, 1) HK_CASE(4, 1) HK_CASE(2, 1) HK_CASE(1, 1)
   HK_CASE(8, 2) HK_CASE(4, 2) HK_CASE(2, 2) HK_CASE(1, 2)
   HK_CASE(8, 4) HK_CASE(4, 4) HK_CASE(2, 4)
 #undef HK_CASE
   return HK_ERR_UNSUPPORTED;
+}
+
+HK_API int hk_gemm_stream(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int rw,
+                          float* workspace, int* counters, int* status, int max_ctas, void* stream) {
+  if (epilogue == EPI_CLAMPGLU) return HK_ERR_UNSUPPORTED;      // that one needs its two numbers: hk_gemm_stream_clamped
+  return gemm_stream_run(a, w, out, M, N, K, ldo, epilogue, rw, workspace, counters, status, max_ctas, GluParams{0.f, 1.f}, stream);
+}
+
+// The gated product with the clamped activation (epilogue 4): out bf16 [M, N/2] = g * sigmoid(slope * g) * (u + 1) with
+// g = min(gate, limit), u = clamp(up, -limit, limit); everything else as for hk_gemm_stream with epilogue 2.
+HK_API int hk_gemm_stream_clamped(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int rw,
+                                  float* workspace, int* counters, int* status, int max_ctas, float limit, float slope,
+                                  void* stream) {
+  return gemm_stream_run(a, w, out, M, N, K, ldo, EPI_CLAMPGLU, rw, workspace, counters, status, max_ctas, GluParams{limit, slope},
+                         stream);
 }
 
 // Floats of workspace a launch may touch: two partial tiles per CTA.

@@ -40,14 +40,23 @@ constexpr int RING_BYTES = 227 * 1024 - 2 * 1024;   // what is left of an SM's s
 constexpr uint32_t TMEM_COLS = 2 * MAX_BN;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GEGLU = 3 };
-// The two gated epilogues differ in the gate's activation alone: silu, or the tanh form of gelu, which is
-// g * sigmoid(2 * sqrt(2 / pi) * (g + 0.044715 g^3)).
-#define IS_GLU(e) ((e) == EPI_SWIGLU || (e) == EPI_GEGLU)
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_GEGLU = 3, EPI_CLAMPGLU = 4 };
+// The first two gated epilogues differ in the gate's activation alone: silu, or the tanh form of gelu, which is
+// g * sigmoid(2 * sqrt(2 / pi) * (g + 0.044715 g^3)).  The third clamps both halves first: with g = min(gate, limit) and
+// u = clamp(up, -limit, limit) it gives g * sigmoid(slope * g) * (u + 1); limit and slope travel as kernel arguments.
+#define IS_GLU(e) ((e) == EPI_SWIGLU || (e) == EPI_GEGLU || (e) == EPI_CLAMPGLU)
+struct GluParams {
+  float limit, slope;
+};
 template <int EPI>
-__device__ __forceinline__ float glu_gate(float g) {
+__device__ __forceinline__ float glu_pair(float g, float u, GluParams gp) {
+  if (EPI == EPI_CLAMPGLU) {
+    g = fminf(g, gp.limit);
+    u = fminf(fmaxf(u, -gp.limit), gp.limit) + 1.0f;
+    return g / (1.0f + __expf(-gp.slope * g)) * u;
+  }
   const float z = EPI == EPI_GEGLU ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
-  return g / (1.0f + __expf(-z));
+  return g / (1.0f + __expf(-z)) * u;
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -202,7 +211,7 @@ __device__ __forceinline__ void load_chunk(const float* o, int c0, float4* y) {
 
 // W gate columns at c0 and their up columns `h` further on -> W bf16 outputs silu(gate) * up.
 template <int W, int EPI>
-__device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, int h, int n_out, bool row_ok, bool vec_ok) {
+__device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, int h, int n_out, bool row_ok, bool vec_ok, GluParams gp) {
   uint32_t g[W], u[W];
   tmem_ld<W>(taddr + (uint32_t)c0, g);
   tmem_ld<W>(taddr + (uint32_t)(h + c0), u);
@@ -215,8 +224,8 @@ __device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, in
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         float g0 = __uint_as_float(g[j + 2 * e]), g1 = __uint_as_float(g[j + 2 * e + 1]);
-        float h0 = glu_gate<EPI>(g0) * __uint_as_float(u[j + 2 * e]);
-        float h1 = glu_gate<EPI>(g1) * __uint_as_float(u[j + 2 * e + 1]);
+        float h0 = glu_pair<EPI>(g0, __uint_as_float(u[j + 2 * e]), gp);
+        float h1 = glu_pair<EPI>(g1, __uint_as_float(u[j + 2 * e + 1]), gp);
         __nv_bfloat162 p = __floats2bfloat162_rn(h0, h1);
         packed[e] = *reinterpret_cast<uint32_t*>(&p);
       }
@@ -226,7 +235,7 @@ __device__ __forceinline__ void swiglu_chunk(uint32_t taddr, bf16* o, int c0, in
     for (int j = 0; j < W; ++j)
       if (c0 + j < n_out) {
         float gv = __uint_as_float(g[j]);
-        o[c0 + j] = __float2bfloat16_rn(glu_gate<EPI>(gv) * __uint_as_float(u[j]));
+        o[c0 + j] = __float2bfloat16_rn(glu_pair<EPI>(gv, __uint_as_float(u[j]), gp));
       }
   }
 }
@@ -238,7 +247,7 @@ template <int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ out,
                int M, int N, int K, long long ldo, int bn, int stages, int splits, float* __restrict__ partial,
-               int* __restrict__ status, const int* __restrict__ groups) {
+               int* __restrict__ status, const int* __restrict__ groups, GluParams gp) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   Control& sm = *reinterpret_cast<Control*>(base);
@@ -392,8 +401,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool vec_ok = (ldo & 7) == 0 && ((nt * h) & 7) == 0;
         int c0 = 0;
 #pragma unroll 1
-        for (; c0 + 32 <= h; c0 += 32) swiglu_chunk<32, EPI>(taddr, o, c0, h, n_out, row_ok, vec_ok);
-        if (c0 < h) swiglu_chunk<16, EPI>(taddr, o, c0, h, n_out, row_ok, vec_ok);
+        for (; c0 + 32 <= h; c0 += 32) swiglu_chunk<32, EPI>(taddr, o, c0, h, n_out, row_ok, vec_ok, gp);
+        if (c0 < h) swiglu_chunk<16, EPI>(taddr, o, c0, h, n_out, row_ok, vec_ok, gp);
       } else {
         const int n0 = nt * bn;
         float* o = reinterpret_cast<float*>(out) + (size_t)row * ldo + n0;
@@ -474,10 +483,10 @@ int sm_count() {
 }
 
 // Adds the K slices of a split product in slice order.  mode 0: out fp32 = sum; 1: out fp32 += sum;
-// 2 (silu) and 3 (tanh gelu): out bf16 [M, N/2] = act(gate) * up, the partial sums' columns in tiles of [bn / 2 gates | their bn / 2 ups].
+// 2 (silu), 3 (tanh gelu) and 4 (clamped): out bf16 [M, N/2] = act(gate) * up, the partial sums' columns in tiles of [bn / 2 gates | their bn / 2 ups].
 template <int MODE>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, int M, int N, long long ldo,
-                                     int splits, int bn) {
+                                     int splits, int bn, GluParams gp) {
   const long long total = MODE >= 2 ? (long long)M * (N / 2) : (long long)M * N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
@@ -494,7 +503,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
       gsum += partial[s * slice + gi];
       usum += partial[s * slice + gi + h];
     }
-    reinterpret_cast<bf16*>(out)[(size_t)m * ldo + j] = __float2bfloat16_rn(glu_gate<MODE>(gsum) * usum);
+    reinterpret_cast<bf16*>(out)[(size_t)m * ldo + j] = __float2bfloat16_rn(glu_pair<MODE>(gsum, usum, gp));
   } else {
     const int m = (int)(i / N), n = (int)(i % N);
     float sum = 0.f;
@@ -532,7 +541,7 @@ __global__ void splitk_reduce_vec_kernel(const float* __restrict__ partial, floa
 
 template <int EPI>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N, int K, long long ldo, int bn, int splits,
-           float* partial, int* status, cudaStream_t s, const int* groups = nullptr) {
+           float* partial, int* status, cudaStream_t s, const int* groups = nullptr, GluParams gp = {0.f, 1.f}) {
   static HkSmemCache allowed = {};
   const uint32_t stage_bytes = stage_bytes_of(bn);
   int stages = RING_BYTES / (int)stage_bytes;
@@ -543,7 +552,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
   const int tiles = ((M + BM - 1) / BM) * n_tiles * splits;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   // dependent launches (measured over decode steps of 24 and 64 rows: 1 % faster; the kernels after this one set up while it drains)
-  int code = hk_launch_pdl(gemm_tc_kernel<EPI>, dim3(grid), dim3(NUM_THREADS), smem, s, ma, mw, out, M, N, K, ldo, bn, stages, splits, partial, status, groups);
+  int code = hk_launch_pdl(gemm_tc_kernel<EPI>, dim3(grid), dim3(NUM_THREADS), smem, s, ma, mw, out, M, N, K, ldo, bn, stages, splits, partial, status, groups, gp);
   if (code != 0 || splits <= 1) return code;
   if (!IS_GLU(EPI) && (N & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)out & 15) == 0) {
     const long long quads = (long long)M * (N / 4);
@@ -552,7 +561,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
   }
   const long long total = IS_GLU(EPI) ? (long long)M * (N / 2) : (long long)M * N;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  return hk_launch_pdl(splitk_reduce_kernel<EPI>, dim3(blocks), dim3(256), 0, s, (const float*)partial, out, M, N, ldo, splits, bn);
+  return hk_launch_pdl(splitk_reduce_kernel<EPI>, dim3(blocks), dim3(256), 0, s, (const float*)partial, out, M, N, ldo, splits, bn, gp);
 }
 
 }  // namespace
@@ -565,11 +574,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* out, int M, int N
 // splits > 1 cuts K into that many slices computed by different CTAs (for few output tiles: decode batches);
 // `partial` must then hold hk_gemm_tc_partial_floats(M, N, splits) floats of scratch; with epilogue 2 the tiles must
 // then fit N exactly ((N / 2) % (bn / 2) == 0).
-HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
-                      int splits, float* partial, int* status, void* stream) {
+static int gemm_tc_run(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
+                       int splits, float* partial, int* status, GluParams gp, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return HK_ERR_UNSUPPORTED;
-  if (epilogue < EPI_STORE || epilogue > EPI_GEGLU) return HK_ERR_UNSUPPORTED;
+  if (epilogue < EPI_STORE || epilogue > EPI_CLAMPGLU) return HK_ERR_UNSUPPORTED;
   if (bn < 16 || bn > MAX_BN || (bn & 15)) return HK_ERR_UNSUPPORTED;
   if (IS_GLU(epilogue) && ((N & 1) || (bn & 31))) return HK_ERR_UNSUPPORTED;
   if (splits < 1 || splits > (K + BK - 1) / BK || (splits > 1 && partial == nullptr)) return HK_ERR_UNSUPPORTED;
@@ -580,7 +589,21 @@ HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int
   if (epilogue == EPI_STORE) return launch<EPI_STORE>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
   if (epilogue == EPI_ADD) return launch<EPI_ADD>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
   if (epilogue == EPI_GEGLU) return launch<EPI_GEGLU>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
+  if (epilogue == EPI_CLAMPGLU) return launch<EPI_CLAMPGLU>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s, nullptr, gp);
   return launch<EPI_SWIGLU>(ma, mw, out, M, N, K, ldo, bn, splits, partial, status, s);
+}
+
+HK_API int hk_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int epilogue, int bn,
+                      int splits, float* partial, int* status, void* stream) {
+  if (epilogue == EPI_CLAMPGLU) return HK_ERR_UNSUPPORTED;      // that one needs its two numbers: hk_gemm_tc_clamped
+  return gemm_tc_run(a, w, out, M, N, K, ldo, epilogue, bn, splits, partial, status, GluParams{0.f, 1.f}, stream);
+}
+
+// The gated product with the clamped activation (epilogue 4): out bf16 [M, N/2] = g * sigmoid(slope * g) * (u + 1) with
+// g = min(gate, limit), u = clamp(up, -limit, limit); everything else as for hk_gemm_tc with epilogue 2.
+HK_API int hk_gemm_tc_clamped(const void* a, const void* w, void* out, int M, int N, int K, long long ldo, int bn, int splits,
+                              float* partial, int* status, float limit, float slope, void* stream) {
+  return gemm_tc_run(a, w, out, M, N, K, ldo, EPI_CLAMPGLU, bn, splits, partial, status, GluParams{limit, slope}, stream);
 }
 
 // Floats of scratch that `hk_gemm_tc` needs for `splits` K slices.

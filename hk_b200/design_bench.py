@@ -583,22 +583,195 @@ def mifolorn_kernel_points(width: int, n: int, decode: bool, peaks: dict) -> dic
     return out
 
 
+def zazulix_shape(width: int, groups: int = 2, vocab: int = 32000, window: int = 1024) -> dict:
+    """Layer sizes that resemble a real model's: a latent attention with heads of 128 over a cached vector of 512 and a
+    window; a differential attention with maps of 64, values of 128, four query heads per key/value head, four taps and
+    whole maps rotated; two retention layers with heads of 64; a dense feed-forward of three times the width and eight
+    experts of half the width in two groups, of which two are used, beside a shared expert."""
+    heads128, heads64 = width // 128, width // 64
+    lat = {"type": "latent_attention", "mixer": {"dim": 128, "heads": heads128, "kv_rank": 512, "vdim": 128, "mask": {"size": window},
+                                                 "scale": 1.0 / math.sqrt(128.0)}}
+    att = {"type": "attention", "mixer": {"dim": 64, "heads": heads128, "kv_heads": max(1, heads128 // 4), "vdim": 128, "conv": 4,
+                                          "diff": 0.5, "rot": {"base": 50000.0, "dims": 64}, "scale": 0.125}}
+    ret = {"type": "retention", "mixer": {"dim": 64, "heads": heads64, "vdim": 64, "rot": {"base": 1000000.0, "dims": 64},
+                                          "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(heads64 - 1, 1)) for h in range(heads64)]}}
+    dense = {"kind": "dense", "ff": 3 * width, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 8, "top": 2, "scale": 2.5, "groups": {"count": 2, "keep": 1}},
+           "shared": {"ff": width // 2}}
+    layers = []
+    for g in range(groups):
+        layers += [dict(lat, mlp=dense), dict(att, mlp=moe), dict(ret, mlp=moe), dict(ret, mlp=moe)]
+    return {"architecture": "Zazulix", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "layers": layers,
+            "initializer_range": 0.02}
+
+
+def zazulix_kernel_points(width: int, n: int, decode: bool, peaks: dict) -> dict:
+    """The design's kernels alone at a layer of this width, each beside the like kernel of the Kedanex (or Mifolorn)
+    decoder: one request of n prompt tokens, or (decode) n requests that each bring one token (the attention over 2,047
+    cached ones; these are timed as replays of a captured graph)."""
+    import numpy as np
+    import torch
+
+    from .csrc import attention_fast, ops
+    dev = "cuda"
+    bw, tc = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    out = {}
+
+    def note(name, us, nbytes, flops, peak_flops, like=None):
+        floor = max(nbytes / bw, flops / peak_flops if peak_flops else 0.0) * 1e6
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "flops": int(flops), "roofline_us": round(floor, 2),
+                     "of_roofline": round(floor / us, 3), **({"like": like} if like else {})}
+
+    count, rows = (n, 1) if decode else (1, n)
+    _time_kernel = lambda fn: globals()["_time_kernel"](fn, replay=decode)      # decode steps replay a captured graph
+    sg = torch.tensor([[i, i * rows, rows] for i in range(count)], dtype=torch.int32, device=dev)
+    fp32 = FP32_TFLOPS * 1e12
+    pt, context = 64, 2047
+    sm = torch.cuda.get_device_properties(0).multi_processor_count
+    per = (context + 1) if decode else n
+    ppr = -(-per // pt)
+    table = torch.arange(count * ppr, dtype=torch.int32, device=dev).view(count, ppr).contiguous()
+    slots = list(range(count))
+    q_starts = list(range(n)) if decode else [0]
+    q_lens = [1] * n if decode else [n]
+    starts = [context] * n if decode else [0]
+    positions = torch.tensor([context] * n if decode else list(range(n)), dtype=torch.int32, device=dev)
+    slot_of = torch.tensor(list(range(n)) if decode else [0] * n, dtype=torch.int32, device=dev)
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    pairs = n * (context + 1) if decode else n * (n + 1) // 2
+
+    # ---- differential attention: convolution, rotation and cache write, the attention itself, the heads' combination
+    H, G, dk, vd, taps = width // 128, max(1, width // 512), 64, 128, 4
+    C = (H + G) * 2 * dk + G * vd
+    proj = torch.randn(n, C + H, device=dev) * 0.5
+    act = torch.empty(n, C, device=dev)
+    conv = torch.randn(C, taps, device=dev) * 0.3
+    tail = torch.zeros(count, taps - 1, C, device=dev)
+    us = _time_kernel(lambda: ops.short_conv(proj[:, :C], conv, sg, tail, act, act="none"))
+    note("short_conv (q, k and v of the differential attention, no activation)", us, n * C * 8 + count * (taps - 1) * C * 8,
+         2.0 * n * C * taps, fp32, like="short_conv (Mifolorn: silu)")
+    us = _time_kernel(lambda: ops.short_conv(proj[:, :C], conv, sg, tail, act))
+    note("short_conv (Mifolorn: silu)", us, n * C * 8 + count * (taps - 1) * C * 8, 2.0 * n * C * taps, fp32)
+    kp = (torch.randn(count * ppr, G, pt, 2 * dk, device=dev) * 0.5).bfloat16()
+    vp = (torch.randn(count * ppr, G, pt, vd, device=dev) * 0.5).bfloat16()
+    q2 = torch.empty(n, 2 * H * 2 * dk, dtype=torch.bfloat16, device=dev)
+    cos = torch.ones(per + 1, dk // 2, device=dev)
+    sin = torch.zeros(per + 1, dk // 2, device=dev)
+    us = _time_kernel(lambda: ops.maps_rope_kv_write(act, q2, cos, sin, dk, positions, slot_of, table, kp, vp, H, G, 2, dk, pt))
+    note("maps_rope_kv_write (two maps a head)", us, n * C * 4 + n * (2 * H * 2 * dk + G * 2 * dk + G * vd) * 2, 0, 0,
+         like="qk_norm_rope_kv_write (Kedanex's attention)")
+    hd = 128
+    qkv = torch.randn(n, (H + 2 * G) * hd, device=dev)
+    q1 = torch.empty(n, H * hd, dtype=torch.bfloat16, device=dev)
+    cos2 = torch.ones(per + 1, hd // 2, device=dev)
+    sin2 = torch.zeros(per + 1, hd // 2, device=dev)
+    us = _time_kernel(lambda: ops.qk_norm_rope_kv_write(qkv, q1, None, None, 1e-5, cos2, sin2, hd, positions, slot_of, table, kp, vp, H, G,
+                                                        hd, pt, norm_after=True))
+    note("qk_norm_rope_kv_write (Kedanex's attention)", us, n * (H + 2 * G) * hd * 6, 0, 0)
+    fixed = attention_fast.decode_splits(n, G, sm) if decode else 0
+
+    def plan_for(heads):
+        rws = 256 if (not decode and attention_fast.tc2_prefill_supported(hd, heads // G, pt)) else (128 if not decode else 64)
+        return attention_fast.build_plan(slots, q_starts, q_lens, starts, n, 0, heads, G, sm, up, fixed_splits=fixed,
+                                         max_context=context + 64 if decode else 0, prefill_rows=rws)
+
+    keys = (n * (context + 1) if decode else n) * G * hd * 4
+    q2.normal_(0.0, 0.5)
+    att2 = torch.empty(n, 2 * H * vd, dtype=torch.bfloat16, device=dev)
+    plan2 = plan_for(2 * H)
+    us = _time_kernel(lambda: ops.paged_attention(q2, kp, vp, table, positions, slot_of, att2, 2 * H, G, hd, pt, 0, 0.125, plan=plan2))
+    # the operations that the design asks for: two maps of dk against the keys, two sums over the values; the kernel
+    # multiplies rows of 2 dk (half of them zeros)
+    note("differential attention (2 H heads over rows of two maps)", us, keys + n * 2 * H * (hd + vd) * 2,
+         (4.0 * dk + 4.0 * vd) * pairs * H, tc, like="attention with a sink (Kedanex; no window here)")
+    q1.normal_(0.0, 0.5)
+    att1 = torch.empty(n, H * hd, dtype=torch.bfloat16, device=dev)
+    plan1 = plan_for(H)
+    us = _time_kernel(lambda: ops.paged_attention(q1, kp, vp, table, positions, slot_of, att1, H, G, hd, pt, 0, hd ** -0.5, plan=plan1,
+                                                  sink=True))
+    note("attention with a sink (Kedanex; no window here)", us, keys + n * H * hd * 4, 4.0 * pairs * H * hd, tc)
+    og = torch.empty(n, H * vd, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.diff_heads_out(att2, proj[:, C:C + H], og, H, vd, 0.5, 1e-6, 0.5))
+    note("diff_heads_out (difference, norm, gate)", us, n * H * vd * 6, 0, 0, like="head_norm_gate (Kedanex)")
+
+    # ---- retention: the scan (its preparation and the walk), the output's norm and gate
+    Hr, dr = width // 64, 64
+    KK = Hr * dr
+    projr = torch.randn(n, 4 * KK, device=dev) * 0.5
+    state = torch.zeros(count, Hr, dr, dr, device=dev)
+    o = torch.empty(n, KK, device=dev)
+    decay = torch.full((Hr,), 0.99, device=dev)
+    cosr = torch.ones(per + 1, dr // 2, device=dev)
+    sinr = torch.zeros(per + 1, dr // 2, device=dev)
+    us = _time_kernel(lambda: ops.retention_scan(projr[:, :KK], projr[:, KK:2 * KK], projr[:, 2 * KK:3 * KK], cosr, sinr, dr, positions, decay,
+                                                 sg, state, o, Hr, dr, dr, dr ** -0.5))
+    note("retention_scan", us, 4 * (4 * n * KK + 2 * count * Hr * dr * dr), 4.0 * n * Hr * dr * dr, fp32, like="delta_rule_scan (Kedanex)")
+    wl = torch.randn(n, KK, device=dev)
+    zb = torch.zeros(KK, device=dev)
+    us = _time_kernel(lambda: ops.delta_rule_scan(projr[:, :KK], projr[:, KK:2 * KK], projr[:, 2 * KK:3 * KK], projr[:, 3 * KK:], wl, zb, zb, sg,
+                                                  state, o, Hr, dr, dr, math.exp(-0.5), 1e-6))
+    note("delta_rule_scan (Kedanex)", us, 4 * (6 * n * KK + 2 * count * Hr * dr * dr), 8.0 * n * Hr * dr * dr, fp32)
+    ogr = torch.empty(n, KK, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.head_out_gate(o, projr[:, 3 * KK:], None, 1e-6, ogr, Hr, dr, act="silu"))
+    note("head_out_gate (retention: no weight, silu)", us, n * KK * (4 + 4 + 2), 0, 0, like="head_norm_gate (Kedanex)")
+    wk = torch.ones(KK, device=dev)
+    us = _time_kernel(lambda: ops.head_norm_gate(o, projr[:, 3 * KK:], wk, 1e-5, ogr, Hr, dr))
+    note("head_norm_gate (Kedanex)", us, n * KK * (4 + 4 + 2), 0, 0)
+
+    # ---- the router with sigmoid scores, groups and the shared expert's gate; the combination with the shared result
+    E, top = 8, 2
+    xb = (torch.randn(n, width, device=dev) * 0.5).bfloat16()
+    wr = torch.randn(E + 1, width, device=dev) * 0.05
+    corr = torch.randn(E, device=dev) * 0.1
+    ids = torch.empty(n, top, dtype=torch.int32, device=dev)
+    wts = torch.empty(n, top, device=dev)
+    sgate = torch.empty(n, 1, device=dev)
+    us = _time_kernel(lambda: ops.route_topk(xb, wr, ids, wts, "sigmoid", corr, 2, 1, 2.5, 1e-20, sgate))
+    note("route_topk (sigmoid scores, correction, groups, shared gate)", us, n * width * 2 + (E + 1) * width * 4, 2.0 * n * (E + 1) * width, fp32,
+         like="route_topk (Kedanex: softmax over the chosen)")
+    wr8 = wr[:E].contiguous()
+    us = _time_kernel(lambda: ops.route_topk(xb, wr8, ids, wts))
+    note("route_topk (Kedanex: softmax over the chosen)", us, n * width * 2 + E * width * 4, 2.0 * n * E * width, fp32)
+    ys = torch.randn(n * top, width, device=dev)
+    inv = torch.randperm(n * top, device=dev).to(torch.int32)
+    res = torch.randn(n, width, device=dev)
+    shared = torch.randn(n, width, device=dev)
+    us = _time_kernel(lambda: ops.route_combine(ys, inv, wts, res, accumulate=True, shared=shared, shared_gate=sgate))
+    note("route_combine (with the gated shared expert)", us, n * width * 4 * (top + 3), 0, 0, like="route_combine (Kedanex)")
+    us = _time_kernel(lambda: ops.route_combine(ys, inv, wts, res, accumulate=True))
+    note("route_combine (Kedanex)", us, n * width * 4 * (top + 2), 0, 0)
+
+    # ---- the dense feed-forward's first product with the clamped activation, beside the one with silu
+    F = 3 * width
+    wgu = (torch.randn(2 * F, width, device=dev) * 0.02).bfloat16()
+    hbuf = torch.empty(n, F, dtype=torch.bfloat16, device=dev)
+    us = _time_kernel(lambda: ops.gemm_swiglu(xb, wgu, hbuf, "swish_clamped", 7.0, 1.702))
+    note("gate/up product with the clamped activation", us, 2 * F * width * 2 + n * (width + F) * 2, 4.0 * n * F * width, tc,
+         like="gate/up product with silu")
+    us = _time_kernel(lambda: ops.gemm_swiglu(xb, wgu, hbuf, "silu"))
+    note("gate/up product with silu", us, 2 * F * width * 2 + n * (width + F) * 2, 4.0 * n * F * width, tc)
+    return out
+
+
 def run(design: str, args, peaks: dict) -> dict:
-    if design not in ("kedanex", "padodra", "mifolorn"):
-        raise SystemExit(f"bench.py --design: unknown design '{design}' (known: kedanex, padodra, mifolorn)")
+    if design not in ("kedanex", "padodra", "mifolorn", "zazulix"):
+        raise SystemExit(f"bench.py --design: unknown design '{design}' (known: kedanex, padodra, mifolorn, zazulix)")
     widths = [int(w) for w in str(args.design_widths).split(",")]
     sizes = {}
     for width in widths:
         t0 = time.time()
-        ours = {"kedanex": kedanex_shape, "padodra": padodra_shape, "mifolorn": mifolorn_shape}[design](width)
+        ours = {"kedanex": kedanex_shape, "padodra": padodra_shape, "mifolorn": mifolorn_shape, "zazulix": zazulix_shape}[design](width)
         runs = len(ours["layers"]) * (ours["loop"]["times"] if "loop" in ours else 1)
-        beside, theirs = ("kedanex", kedanex_shape(width, runs // 4)) if design == "mifolorn" else ("qwen3", qwen3_shape(width, runs))
+        beside, theirs = ("kedanex", kedanex_shape(width, runs // 4)) if design in ("mifolorn", "zazulix") else ("qwen3", qwen3_shape(width, runs))
         entry = {design: model_points(ours, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
                  beside: model_points(theirs, 2048, (8, 64), args.steps, max(args.warmup, 3), 5),
                  "layer_runs": runs}
         if design == "mifolorn":
             entry["kernels_prefill_2048_rows"] = mifolorn_kernel_points(width, 2048, False, peaks)
             entry["kernels_decode_64_rows"] = mifolorn_kernel_points(width, 64, True, peaks)
+        elif design == "zazulix":
+            entry["kernels_prefill_2048_rows"] = zazulix_kernel_points(width, 2048, False, peaks)
+            entry["kernels_decode_64_rows"] = zazulix_kernel_points(width, 64, True, peaks)
         elif design == "kedanex":
             entry["kernels_prefill_2048_rows"] = kernel_points(width, 2048, peaks)
             entry["kernels_decode_64_rows"] = {k: v for k, v in kernel_points(width, 64, peaks).items() if "request" not in k or "decode" in k}
@@ -609,7 +782,7 @@ def run(design: str, args, peaks: dict) -> dict:
         sizes[f"width{width}"] = entry
         print(f"[bench] design {design}, width {width}: {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
     k = sizes[f"width{widths[-1]}"]
-    return {"metric": f"{design} prefill and decode tok/s beside {'Kedanex' if design == 'mifolorn' else 'Qwen3'} at equal width and depth", "value": k[design]["decode_b8"]["tok_s"],
+    return {"metric": f"{design} prefill and decode tok/s beside {'Kedanex' if design in ('mifolorn', 'zazulix') else 'Qwen3'} at equal width and depth", "value": k[design]["decode_b8"]["tok_s"],
             "unit": "tokens/s (decode, batch 8, largest width)", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "higher_is_better": True, "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
             "impl": "ours", "design": design, "sizes": sizes, "peaks": peaks}

@@ -40,6 +40,8 @@ def diff_part(d, H, G, dk, dv, taps, rot, diff=0.4, scale=None, window=None):
     (24, 2, 2, 12, 10, 0, {"base": 50.0, "dims": 12}),       # values narrower than two maps, no convolution, G = H
     (32, 3, 1, 6, 20, 1, {"base": 100.0, "dims": 2}),        # values wider than two maps, one tap
     (32, 1, 1, 24, 24, 5, {"base": 3000.0, "dims": 8}),      # one head
+    (64, 4, 2, 48, 96, 3, {"base": 50000.0, "dims": 16}),    # rows of 96: the mma.sync kernels for prompts too
+    (64, 8, 2, 64, 128, 4, {"base": 50000.0, "dims": 64}),   # rows of 128, eight rows a group
 ])
 def test_differential_attention_under_every_cut(dtype, d, H, G, dk, dv, taps, rot):
     part, m = diff_part(d, H, G, dk, dv, taps, rot)
@@ -51,9 +53,9 @@ def test_differential_attention_under_every_cut(dtype, d, H, G, dk, dv, taps, ro
 @pytest.mark.parametrize("dk,dv", [(32, 64), (12, 20)])
 def test_differential_attention_finds_one_key_among_hundreds(dtype, dk, dv):
     """The first map's query reads the input as its key does, eight times as large, the convolution passes the current
-    token alone and nothing is rotated: a token looks at the tokens whose input resembles its own.  The last three tokens
-    repeat the inputs at positions 3, 15 (a page's last row) and 16 (a page's first), 400 tokens back; without those keys
-    the result is another one."""
+    token alone and nothing is rotated: a token looks at the tokens whose input resembles its own.  Queries and keys read
+    the first half of the input, values the second.  The last three tokens repeat the first half of the inputs at positions
+    3, 15 (a page's last row) and 16 (a page's first), 400 tokens back; without those keys the result is another one."""
     d, H, G, taps, T = 48, 2, 1, 3, 420
     part, m = diff_part(d, H, G, dk, dv, taps, None, scale=1.0 / dk)
     prec, w = bind_random(part, dtype, std=0.25)
@@ -61,16 +63,21 @@ def test_differential_attention_finds_one_key_among_hundreds(dtype, dk, dv):
         wk = part.w_in[H * 2 * dk:H * 2 * dk + dk].clone()          # key head 0, map 1
         for h in range(H):
             part.w_in[h * 2 * dk:h * 2 * dk + dk] = wk * 8.0
+        part.w_in[:(H + G) * 2 * dk, d // 2:] = 0
+        part.w_in[(H + G) * 2 * dk:(H + G) * 2 * dk + G * dv, :d // 2] = 0
         part.conv.weight.zero_()
         part.conv.weight[:, -1] = 1.0
     for h in range(H):
         w["m.q"][h * 2 * dk:h * 2 * dk + dk] = w["m.k"][:dk] * 8.0
+    w["m.q"][:, d // 2:] = 0
+    w["m.k"][:, d // 2:] = 0
+    w["m.v"][:, :d // 2] = 0
     for c in ("q", "k", "v"):
         w[f"m.{c}.conv"] = np.zeros_like(w[f"m.{c}.conv"])
         w[f"m.{c}.conv"][:, -1] = 1.0
     x = torch.randn(T, d, device="cuda")
     for i, src in enumerate((3, 15, 16)):
-        x[T - 3 + i] = x[src]
+        x[T - 3 + i, :d // 2] = x[src, :d // 2]
     x = x.to(dtype)
     xs = x.double().cpu().numpy()
     want = P.differential_attention(xs, w, "m.", m, 1e-5)
@@ -178,8 +185,11 @@ def test_short_convolution_without_activation_across_the_edges_of_portions(taps)
 # ------------------------------------------------------------------------------------ feed-forwards
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("d,F,limit,rows", [(40, 52, 0.7, 9), (64, 160, 1.0, 70), (128, 320, 2.5, 300)])
+@pytest.mark.parametrize("d,F,limit,rows", [(40, 52, 0.7, 9), (64, 160, 1.0, 70), (128, 320, 2.5, 300), (128, 320, 1.5, 12),
+                                            (192, 256, 1.0, 5), (256, 1024, 1.2, 2048)])
 def test_clamped_feed_forward(dtype, d, F, limit, rows):
+    """Rows and sizes that reach every kernel with the activation in its epilogue (the generic product with the
+    activation's own kernel, the streaming product, the tcgen05 product with and without K slices)."""
     from hk_b200.parts import SwiGLUFeedForward
     part = SwiGLUFeedForward(d, F, "f.", act="swish_clamped", names={"gate": "gate", "up": "up", "down": "down"}, limit=limit, slope=1.702)
     prec, w = bind_random(part, dtype, std=0.2)

@@ -277,9 +277,24 @@ def test_trace_run_program(tmp_path_factory, tmp_path, dtype):
             pos[rid] = pos.get(rid, 0) + len(toks)
     if tdt == torch.float32:
         compare(got, ref, seqs, tdt)
-    else:       # without the engine's choices at hand: twice what rounding alone does along the plain choices
-        slack = {rid: 2 * centred_rms(plain_along(cfg, weights, ids, None, rounded=True) - ref[rid]) for rid, ids in seqs.items()}
-        compare(got, ref, seqs, tdt, slack)
+        return
+    # The engine's choices are not at hand here.  A request is compared up to its first token at which some router's
+    # choice was close (from there on the engine may rightly have gone another way); most positions remain.
+    kept_seqs, kept_ref, kept_got, slack = {}, {}, {}, {}
+    for rid, ids in seqs.items():
+        P.route_margins = margins = {}
+        try:
+            P.forward(cfg, weights, ids)
+        finally:
+            P.route_margins = None
+        closest = np.min(np.stack(list(margins.values())), axis=0)
+        n = int(np.argmax(closest < CLOSE_CALL)) if (closest < CLOSE_CALL).any() else len(ids)
+        if n:
+            kept_seqs[rid], kept_ref[rid] = ids[:n], ref[rid][:n]
+            slack[rid] = 2 * centred_rms(plain_along(cfg, weights, ids, None, rounded=True) - ref[rid])[:n]
+            kept_got.update({(rid, p): got[(rid, p)] for p in range(n)})
+    assert len(kept_got) >= 0.4 * len(got)
+    compare(kept_got, kept_ref, kept_seqs, tdt, slack)
 
 
 def test_command_line_generates_with_this_design(tmp_path_factory):
