@@ -635,12 +635,14 @@ HK_API int hk_gated_delta_scan(const float* q, const float* k, const float* v, l
 // Linear attention with a fixed decay per head and neither softmax nor denominator:
 //     S <- decay_h S + k v^T;   o = S^T q
 // q and k [n, H * dk] are first turned by position on their first `rot` dims (dim i paired with i + rot / 2, angle from
-// the tables cos, sin [positions, rot / 2]; rot = 0: no rotation), k then times k_scale.  As a record of the generalised
-// rule it is (d, a*u, u, k, r, v) = (decay_h, 0, 0, k, q, v): the scan above runs it.
+// the tables cos, sin [positions, rot / 2]; rot = 0: no rotation), k then times k_scale.  The preparation writes, per
+// (token, head), either the lean record [k | q | v] (2 P + dv floats, the vectors in the scan's lane layout) for the scan
+// below, or (value sizes that are no multiple of 4) the generalised rule's record (d, a*u, u, k, r, v) =
+// (decay_h, 0, 0, k, q, v), which that rule's plain scan runs.
 __global__ void retention_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                                       long long ld, const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
                                       const int* __restrict__ positions, const float* __restrict__ decay, float* __restrict__ rec,
-                                      long long items, int H, int dk, int dv, int L, int RPT, float k_scale) {
+                                      long long items, int H, int dk, int dv, int L, int RPT, float k_scale, int lean) {
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (item >= items) return;
@@ -653,12 +655,11 @@ __global__ void retention_prep_kernel(const float* __restrict__ q, const float* 
   const float* s = sin_t + (size_t)positions[row] * half;
   const float dec = decay[h];
   const int P = L * RPT;
-  float* out = rec + (size_t)item * (5 * P + dv);
+  float* out = rec + (size_t)item * ((lean ? 2 : 5) * P + dv);
   for (int j = lane; j < P; j += 32) {
     const int i = (j % RPT) * L + j / RPT;       // the entry that sits at place j
-    float d = 0.f, kv = 0.f, qv = 0.f;
+    float kv = 0.f, qv = 0.f;
     if (i < dk) {
-      d = dec;
       if (i < half) {
         kv = kp[i] * c[i] - kp[i + half] * s[i];
         qv = qp[i] * c[i] - qp[i + half] * s[i];
@@ -671,17 +672,149 @@ __global__ void retention_prep_kernel(const float* __restrict__ q, const float* 
       }
       kv *= k_scale;
     }
-    out[j] = d;
-    out[P + j] = 0.f;
-    out[2 * P + j] = 0.f;
-    out[3 * P + j] = kv;
-    out[4 * P + j] = qv;
+    if (lean) {
+      out[j] = kv;
+      out[P + j] = qv;
+    } else {
+      out[j] = i < dk ? dec : 0.f;
+      out[P + j] = 0.f;
+      out[2 * P + j] = 0.f;
+      out[3 * P + j] = kv;
+      out[4 * P + j] = qv;
+    }
   }
-  for (int cidx = lane; cidx < dv; cidx += 32) out[5 * P + cidx] = v[row * ld + (size_t)h * dv + cidx];
+  float* vo = out + (lean ? 2 : 5) * P;
+  for (int cidx = lane; cidx < dv; cidx += 32) vo[cidx] = v[row * ld + (size_t)h * dv + cidx];
+}
+
+// The scan over lean records: the delta rule's layout of the state (a block owns `cols` columns of one head's state for
+// one segment, a column's entries spread over L lanes, RPT per lane, in registers; records through a two-stage cp.async
+// ring), but the chain that the next token waits for is one multiply and one fused multiply-add per state entry: no dot
+// product with the old state, no shuffle before the update.  The read-out's dot product hangs off that chain.
+template <int RPT, int L, int CPT>
+__global__ void __launch_bounds__(256)
+retention_scan_kernel(const float* __restrict__ rec, const int* __restrict__ segs, const float* __restrict__ decay,
+                      float* __restrict__ state, float* __restrict__ out, int H, int dk, int dv, int cols, int chunk) {
+  extern __shared__ __align__(16) float sm[];   // [2][chunk][2 P + dv]
+  constexpr int P = L * RPT;
+  const int R = 2 * P + dv;
+  const int seg = blockIdx.x / H, h = blockIdx.x % H;
+  const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
+  const int col0 = blockIdx.y * cols;
+  const int tid = threadIdx.x;
+  const int sub = tid % L, cidx = (tid / L) * CPT;
+  const float dec = decay[h];
+  bool col_ok[CPT];
+  int col[CPT];
+  float S[CPT][RPT];
+  float* sp = state + ((size_t)slot * H + h) * dk * dv;
+#pragma unroll
+  for (int c = 0; c < CPT; ++c) {
+    col[c] = col0 + cidx + c;
+    col_ok[c] = cidx + c < cols && col[c] < dv;
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+      const int i = sub + L * m;
+      S[c][m] = (col_ok[c] && i < dk) ? sp[(size_t)i * dv + col[c]] : 0.f;
+    }
+  }
+  const int pieces = R >> 2;                    // records are whole 16-byte pieces: P is a multiple of 8, dv of 4
+  auto fetch = [&](int c) {                     // chunk c -> stage c & 1
+    const int t0 = c * chunk, tc = min(chunk, count - t0);
+    float* dst = sm + (size_t)(c & 1) * chunk * R;
+    const float* src = rec + ((size_t)(row0 + t0) * H + h) * R;
+    for (int t = 0; t < tc; ++t)
+      for (int p = tid; p < pieces; p += blockDim.x) dr_cp_async16(dst + (size_t)t * R + 4 * p, src + (size_t)t * H * R + 4 * p);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int nchunks = (count + chunk - 1) / chunk;
+  float* op = out + (size_t)row0 * H * dv + (size_t)h * dv + col[0];
+  const size_t ostep = (size_t)H * dv;
+  const bool lead = sub == 0;
+  const int mine = sub * RPT, vat = 2 * P + min(col[0], dv - CPT);
+  fetch(0);
+  for (int c = 0; c < nchunks; ++c) {
+    if (c + 1 < nchunks) {
+      fetch(c + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int tc = min(chunk, count - c * chunk);
+    const float* buf = sm + (size_t)(c & 1) * chunk * R + mine;
+    const float* vbuf = sm + (size_t)(c & 1) * chunk * R + vat;
+#pragma unroll 2
+    for (int t = 0; t < tc; ++t) {
+      const float* tok = buf + (size_t)t * R;
+      float v[CPT], acc[CPT][2];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        v[cc] = vbuf[(size_t)t * R + cc];
+        acc[cc][0] = acc[cc][1] = 0.f;
+      }
+#pragma unroll
+      for (int q = 0; q < RPT / 4; ++q) {
+        const float4 k = *reinterpret_cast<const float4*>(tok + 4 * q);
+        const float4 r = *reinterpret_cast<const float4*>(tok + P + 4 * q);
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          float* Sc = S[cc];
+          Sc[4 * q] = fmaf(k.x, v[cc], dec * Sc[4 * q]);
+          Sc[4 * q + 1] = fmaf(k.y, v[cc], dec * Sc[4 * q + 1]);
+          Sc[4 * q + 2] = fmaf(k.z, v[cc], dec * Sc[4 * q + 2]);
+          Sc[4 * q + 3] = fmaf(k.w, v[cc], dec * Sc[4 * q + 3]);
+          acc[cc][0] = fmaf(r.y, Sc[4 * q + 1], fmaf(r.x, Sc[4 * q], acc[cc][0]));
+          acc[cc][1] = fmaf(r.w, Sc[4 * q + 3], fmaf(r.z, Sc[4 * q + 2], acc[cc][1]));
+        }
+      }
+      float o_[CPT];
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) o_[cc] = acc[cc][0] + acc[cc][1];
+#pragma unroll
+      for (int o = L >> 1; o > 0; o >>= 1)
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) o_[cc] += __shfl_xor_sync(0xffffffffu, o_[cc], o);
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc)
+        if (lead && col_ok[cc]) op[(size_t)t * ostep + cc] = o_[cc];
+    }
+    op += (size_t)tc * ostep;
+    __syncthreads();                            // the stage may be filled again
+  }
+#pragma unroll
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int m = 0; m < RPT; ++m) {
+      const int i = sub + L * m;
+      if (col_ok[c] && i < dk) sp[(size_t)i * dv + col[c]] = S[c][m];
+    }
+}
+
+template <int RPT, int CPT>
+static int ret_launch(int L, dim3 grid, int threads, size_t smem, cudaStream_t s, const float* rec, const int* segs,
+                      const float* decay, float* state, float* out, int H, int dk, int dv, int cols, int chunk) {
+#define RET_LAUNCH(LL)                                                                                                      \
+  do {                                                                                                                      \
+    static HkSmemCache cache;                                                                                               \
+    int e = hk_allow_smem(retention_scan_kernel<RPT, LL, CPT>, smem, cache);                                                \
+    if (e) return e;                                                                                                        \
+    return hk_launch(retention_scan_kernel<RPT, LL, CPT>, grid, dim3(threads), smem, s, rec, segs, decay, state, out, H, dk, dv, \
+                     cols, chunk);                                                                                          \
+  } while (0)
+  switch (L) {
+    case 1: RET_LAUNCH(1);
+    case 2: RET_LAUNCH(2);
+    case 4: RET_LAUNCH(4);
+    case 8: RET_LAUNCH(8);
+    case 16: RET_LAUNCH(16);
+    default: RET_LAUNCH(32);
+  }
+#undef RET_LAUNCH
 }
 
 // q, k [n, H*dk] and v [n, H*dv] are column slices of one float32 matrix (row stride ld); decay float32 [H]; `rec` as for
-// hk_delta_rule_scan.
+// hk_delta_rule_scan.  Blocks, columns a block and columns a lane group are chosen as for the delta rule's scan.
 HK_API int hk_retention_scan(const float* q, const float* k, const float* v, long long ld, const float* cos_t, const float* sin_t,
                              int rot, const int* positions, const float* decay, const int* segs, int n_seg, int n_rows, float* rec,
                              float* state, float* out, int H, int dk, int dv, float k_scale, void* stream) {
@@ -691,10 +824,26 @@ HK_API int hk_retention_scan(const float* q, const float* k, const float* v, lon
   int L, rpt;
   if (!dr_plan(n_seg, H, dk, dv, &L, &rpt)) return HK_ERR_UNSUPPORTED;
   const long long items = (long long)n_rows * H;
+  const int lean = (dv & 3) == 0;
   int e = hk_launch(retention_prep_kernel, dim3((unsigned)((items + 7) / 8)), dim3(256), 0, s, q, k, v, ld, cos_t, sin_t, rot,
-                    positions, decay, rec, items, H, dk, dv, L, rpt, k_scale);
+                    positions, decay, rec, items, H, dk, dv, L, rpt, k_scale, lean);
   if (e) return e;
-  return dr_scan_records(rec, segs, n_seg, state, out, H, dk, dv, L, rpt, s);
+  if (!lean) return dr_scan_records(rec, segs, n_seg, state, out, H, dk, dv, L, rpt, s);
+  const int R = 2 * L * rpt + dv;
+  int cols = max(1, min(dv, 256 / L));
+  while (cols > 8 && cols * L > 64 && (long long)n_seg * H * ((dv + cols - 1) / cols) < 2 * 148) cols >>= 1;
+  const bool many = (long long)n_seg * H * ((dv + cols - 1) / cols) >= 2 * 148;
+  const int cpt = (rpt == 8 && many && (cols & 1) == 0 && (dv & 1) == 0) ? 2 : 1;
+  const int threads = ((cols / cpt * L + 31) / 32) * 32;
+  int chunk = 16;
+  while (chunk > 2 && (size_t)2 * chunk * R * sizeof(float) > 64 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * chunk * R * sizeof(float);
+  dim3 grid((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols));
+  if (rpt == 8 && cpt == 2) return ret_launch<8, 2>(L, grid, threads, smem, s, rec, segs, decay, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 8) return ret_launch<8, 1>(L, grid, threads, smem, s, rec, segs, decay, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 16) return ret_launch<16, 1>(L, grid, threads, smem, s, rec, segs, decay, state, out, H, dk, dv, cols, chunk);
+  if (rpt == 32) return ret_launch<32, 1>(L, grid, threads, smem, s, rec, segs, decay, state, out, H, dk, dv, cols, chunk);
+  return ret_launch<64, 1>(L, grid, threads, smem, s, rec, segs, decay, state, out, H, dk, dv, cols, chunk);
 }
 
 // ------------------------------------------------------------------ matrix memory with exponential gates (mLSTM)

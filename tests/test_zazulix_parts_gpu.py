@@ -76,6 +76,9 @@ def test_differential_attention_finds_one_key_among_hundreds(dtype, dk, dv):
         w[f"m.{c}.conv"] = np.zeros_like(w[f"m.{c}.conv"])
         w[f"m.{c}.conv"][:, -1] = 1.0
     x = torch.randn(T, d, device="cuda")
+    quiet = torch.ones(T, 1, device="cuda") * 0.3          # every other token's key is small, so that none competes
+    quiet[[3, 15, 16]] = 1.0
+    x[:, :d // 2] *= quiet
     for i, src in enumerate((3, 15, 16)):
         x[T - 3 + i, :d // 2] = x[src, :d // 2]
     x = x.to(dtype)

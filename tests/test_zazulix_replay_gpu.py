@@ -278,23 +278,18 @@ def test_trace_run_program(tmp_path_factory, tmp_path, dtype):
     if tdt == torch.float32:
         compare(got, ref, seqs, tdt)
         return
-    # The engine's choices are not at hand here.  A request is compared up to its first token at which some router's
-    # choice was close (from there on the engine may rightly have gone another way); most positions remain.
-    kept_seqs, kept_ref, kept_got, slack = {}, {}, {}, {}
-    for rid, ids in seqs.items():
-        P.route_margins = margins = {}
-        try:
-            P.forward(cfg, weights, ids)
-        finally:
-            P.route_margins = None
-        closest = np.min(np.stack(list(margins.values())), axis=0)
-        n = int(np.argmax(closest < CLOSE_CALL)) if (closest < CLOSE_CALL).any() else len(ids)
-        if n:
-            kept_seqs[rid], kept_ref[rid] = ids[:n], ref[rid][:n]
-            slack[rid] = 2 * centred_rms(plain_along(cfg, weights, ids, None, rounded=True) - ref[rid])[:n]
-            kept_got.update({(rid, p): got[(rid, p)] for p in range(n)})
-    assert len(kept_got) >= 0.4 * len(got)
-    compare(kept_got, kept_ref, kept_seqs, tdt, slack)
+    # The engine's choices are not at hand here, and a close call of a router may fall the other way than in the plain
+    # implementation (the tests above follow the engine's choices).  The program must give what an engine gives that is
+    # set up and driven as the program does it: the same kernels on the same numbers.
+    from hk_b200.engine import Engine
+    max_tokens = helpers.peak_tokens(steps)
+    engine = Engine(d, dtype=dtype, max_tokens=max_tokens, page_tokens=16, max_requests=4, max_context=max_tokens,
+                    max_batch_tokens=max_tokens)
+    same = helpers.run_trace_on_engine(engine, steps)
+    assert set(same) == set(got)
+    scale = max(np.abs(r).max() for r in ref.values())
+    off = [key for key in got if np.abs(got[key] - same[key]).max() > 1e-3 * scale]
+    assert len(off) <= 0.03 * len(got), f"{len(off)} of {len(got)} positions differ from the engine's own, the first {sorted(off)[0]}"
 
 
 def test_command_line_generates_with_this_design(tmp_path_factory):
