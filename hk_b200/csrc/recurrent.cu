@@ -690,14 +690,18 @@ __global__ void retention_prep_kernel(const float* __restrict__ q, const float* 
 // The scan over lean records: the delta rule's layout of the state (a block owns `cols` columns of one head's state for
 // one segment, a column's entries spread over L lanes, RPT per lane, in registers; records through a two-stage cp.async
 // ring), but the chain that the next token waits for is one multiply and one fused multiply-add per state entry: no dot
-// product with the old state, no shuffle before the update.  The read-out's dot product hangs off that chain.
+// product with the old state, no shuffle before the update.  The read-out's dot product hangs off that chain, and its sum
+// over a column's L lanes is put off: every lane leaves its share of a token's output in shared memory, and after a chunk
+// of tokens the block adds the shares (lane 0 first, in order) and writes the chunk's outputs, neighbours side by side.
 template <int RPT, int L, int CPT>
 __global__ void __launch_bounds__(256)
 retention_scan_kernel(const float* __restrict__ rec, const int* __restrict__ segs, const float* __restrict__ decay,
                       float* __restrict__ state, float* __restrict__ out, int H, int dk, int dv, int cols, int chunk) {
-  extern __shared__ __align__(16) float sm[];   // [2][chunk][2 P + dv]
+  extern __shared__ __align__(16) float sm[];   // [2][chunk][2 P + dv] records, then [2][chunk][W] the lanes' shares
   constexpr int P = L * RPT;
   const int R = 2 * P + dv;
+  const int W = blockDim.x * CPT;               // shares a token: one per (column of the block, lane)
+  float* part = sm + (size_t)2 * chunk * R;
   const int seg = blockIdx.x / H, h = blockIdx.x % H;
   const int slot = segs[seg * 3], row0 = segs[seg * 3 + 1], count = segs[seg * 3 + 2];
   const int col0 = blockIdx.y * cols;
@@ -728,9 +732,9 @@ retention_scan_kernel(const float* __restrict__ rec, const int* __restrict__ seg
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const int nchunks = (count + chunk - 1) / chunk;
-  float* op = out + (size_t)row0 * H * dv + (size_t)h * dv + col[0];
+  float* op = out + (size_t)row0 * H * dv + (size_t)h * dv + col0;
   const size_t ostep = (size_t)H * dv;
-  const bool lead = sub == 0;
+  const int ncols = min(cols, dv - col0);       // columns of this block that exist
   const int mine = sub * RPT, vat = 2 * P + min(col[0], dv - CPT);
   fetch(0);
   for (int c = 0; c < nchunks; ++c) {
@@ -744,7 +748,8 @@ retention_scan_kernel(const float* __restrict__ rec, const int* __restrict__ seg
     const int tc = min(chunk, count - c * chunk);
     const float* buf = sm + (size_t)(c & 1) * chunk * R + mine;
     const float* vbuf = sm + (size_t)(c & 1) * chunk * R + vat;
-#pragma unroll 2
+    float* pw = part + (size_t)(c & 1) * chunk * W + (size_t)cidx * L + sub;
+#pragma unroll 4
     for (int t = 0; t < tc; ++t) {
       const float* tok = buf + (size_t)t * R;
       float v[CPT], acc[CPT][2];
@@ -768,19 +773,22 @@ retention_scan_kernel(const float* __restrict__ rec, const int* __restrict__ seg
           acc[cc][1] = fmaf(r.w, Sc[4 * q + 3], fmaf(r.z, Sc[4 * q + 2], acc[cc][1]));
         }
       }
-      float o_[CPT];
 #pragma unroll
-      for (int cc = 0; cc < CPT; ++cc) o_[cc] = acc[cc][0] + acc[cc][1];
+      for (int cc = 0; cc < CPT; ++cc) pw[(size_t)t * W + cc * L] = acc[cc][0] + acc[cc][1];
+    }
+    __syncthreads();                            // the shares are written; the stage may be filled again
+    // (the shares of chunk c + 2 go to this buffer again, behind the barrier of chunk c + 1, which every thread reaches
+    // only after it has read what it needs here)
+    const float* pr = part + (size_t)(c & 1) * chunk * W;
+    for (int e = tid; e < tc * ncols; e += blockDim.x) {
+      const int t = e / ncols, cl = e % ncols;
+      const float* shares = pr + (size_t)t * W + (size_t)cl * L;
+      float sum = shares[0];
 #pragma unroll
-      for (int o = L >> 1; o > 0; o >>= 1)
-#pragma unroll
-        for (int cc = 0; cc < CPT; ++cc) o_[cc] += __shfl_xor_sync(0xffffffffu, o_[cc], o);
-#pragma unroll
-      for (int cc = 0; cc < CPT; ++cc)
-        if (lead && col_ok[cc]) op[(size_t)t * ostep + cc] = o_[cc];
+      for (int l = 1; l < L; ++l) sum += shares[l];
+      op[(size_t)t * ostep + cl] = sum;
     }
     op += (size_t)tc * ostep;
-    __syncthreads();                            // the stage may be filled again
   }
 #pragma unroll
   for (int c = 0; c < CPT; ++c)
@@ -836,8 +844,8 @@ HK_API int hk_retention_scan(const float* q, const float* k, const float* v, lon
   const int cpt = (rpt == 8 && many && (cols & 1) == 0 && (dv & 1) == 0) ? 2 : 1;
   const int threads = ((cols / cpt * L + 31) / 32) * 32;
   int chunk = 16;
-  while (chunk > 2 && (size_t)2 * chunk * R * sizeof(float) > 64 * 1024) chunk >>= 1;
-  const size_t smem = (size_t)2 * chunk * R * sizeof(float);
+  while (chunk > 2 && (size_t)2 * chunk * (R + threads * cpt) * sizeof(float) > 64 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * chunk * (R + threads * cpt) * sizeof(float);       // records, and the lanes' shares of the outputs
   dim3 grid((unsigned)(n_seg * H), (unsigned)((dv + cols - 1) / cols));
   if (rpt == 8 && cpt == 2) return ret_launch<8, 2>(L, grid, threads, smem, s, rec, segs, decay, state, out, H, dk, dv, cols, chunk);
   if (rpt == 8) return ret_launch<8, 1>(L, grid, threads, smem, s, rec, segs, decay, state, out, H, dk, dv, cols, chunk);

@@ -592,8 +592,8 @@ def zazulix_shape(width: int, groups: int = 2, vocab: int = 32000, window: int =
     lat = {"type": "latent_attention", "mixer": {"dim": 128, "heads": heads128, "kv_rank": 512, "vdim": 128, "mask": {"size": window},
                                                  "scale": 1.0 / math.sqrt(128.0)}}
     att = {"type": "attention", "mixer": {"dim": 64, "heads": heads128, "kv_heads": max(1, heads128 // 4), "vdim": 128, "conv": 4,
-                                          "diff": 0.5, "rot": {"base": 50000.0, "dims": 64}, "scale": 0.125}}
-    ret = {"type": "retention", "mixer": {"dim": 64, "heads": heads64, "vdim": 64, "rot": {"base": 1000000.0, "dims": 64},
+                                          "diff": 0.4, "rot": {"base": 100000.0, "dims": 64}, "scale": 0.125}}
+    ret = {"type": "retention", "mixer": {"dim": 64, "heads": heads64, "vdim": 64, "rot": {"base": 500000.0, "dims": 32},
                                           "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(heads64 - 1, 1)) for h in range(heads64)]}}
     dense = {"kind": "dense", "ff": 3 * width, "limit": 7.0}
     moe = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 8, "top": 2, "scale": 2.5, "groups": {"count": 2, "keep": 1}},

@@ -36,7 +36,7 @@ def diff_part(d, H, G, dk, dv, taps, rot, diff=0.4, scale=None, window=None):
 @pytest.mark.parametrize("d,H,G,dk,dv,taps,rot", [
     (40, 4, 2, 8, 16, 3, {"base": 900.0, "dims": 4}),        # cache rows of 16: the tensor-core kernels' smallest head
     (48, 6, 2, 16, 32, 4, None),                             # rows of 32, three heads a group, no rotation
-    (64, 2, 1, 32, 64, 2, {"base": 10000.0, "dims": 32}),    # rows of 64: the tcgen05 prompt kernel
+    (64, 2, 1, 32, 64, 2, {"base": 10000.0, "dims": 20}),    # rows of 64: the tcgen05 prompt kernel
     (24, 2, 2, 12, 10, 0, {"base": 50.0, "dims": 12}),       # values narrower than two maps, no convolution, G = H
     (32, 3, 1, 6, 20, 1, {"base": 100.0, "dims": 2}),        # values wider than two maps, one tap
     (32, 1, 1, 24, 24, 5, {"base": 3000.0, "dims": 8}),      # one head
@@ -94,7 +94,7 @@ def test_differential_attention_finds_one_key_among_hundreds(dtype, dk, dv):
 # ------------------------------------------------------------------------------------ latent attention over a window
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("d,H,dk,dv,r,window", [(40, 3, 8, 12, 16, 7), (64, 8, 32, 32, 64, 40), (48, 2, 16, 8, 24, 33),
+@pytest.mark.parametrize("d,H,dk,dv,r,window", [(40, 3, 8, 12, 16, 7), (64, 8, 32, 48, 64, 37), (48, 2, 16, 8, 24, 33),
                                                 (40, 5, 6, 10, 10, None), (64, 4, 16, 48, 144, 21), (32, 1, 8, 8, 32, 1)])
 def test_latent_attention_without_positions_over_a_window(dtype, d, H, dk, dv, r, window):
     """Sharp scores (a large factor), so that a token's result hangs on few keys: a window that is one token off shows at
@@ -120,7 +120,7 @@ def test_latent_attention_without_positions_over_a_window(dtype, d, H, dk, dv, r
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("d,H,dk,dv,rot,decay", [
     (40, 3, 8, 12, {"base": 10000.0, "dims": 8}, [0.9, 0.97, 0.995]), (48, 2, 24, 8, {"base": 50000.0, "dims": 12}, [0.96, 0.999]),
-    (64, 2, 64, 64, {"base": 1000000.0, "dims": 64}, [0.984375, 0.9990234375]), (40, 3, 10, 6, None, [0.8, 0.9, 0.95]),
+    (64, 2, 64, 64, {"base": 200000.0, "dims": 64}, [0.98, 0.999]), (40, 3, 10, 6, None, [0.8, 0.9, 0.95]),
     (32, 1, 136, 7, {"base": 100.0, "dims": 2}, [1.0]), (32, 4, 8, 16, {"base": 500.0, "dims": 6}, [0.5, 0.9, 0.99, 1.0])])
 def test_retention_under_every_cut(dtype, d, H, dk, dv, rot, decay):
     from hk_b200.parts import Retention
@@ -221,7 +221,7 @@ def routed_part(d, F, E, top, scale, groups, shared):
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("d,F,E,top,scale,groups,shared,rows,shift", [
     (40, 12, 6, 1, 2.5, (6, 2), 20, 33, 0.0),          # groups of one expert
-    (48, 24, 12, 4, 1.5, (2, 1), 40, 57, -3.0),        # every choice score negative: a refused group must not count as 0
+    (48, 24, 10, 3, 1.3, (2, 1), 40, 57, -3.0),        # every choice score negative: a refused group must not count as 0
     (64, 32, 9, 3, 2.0, (3, 2), 0, 300, 0.0),          # no shared expert; prompt-sized rows
     (32, 16, 4, 4, 1.0, (2, 2), 24, 20, 0.5),          # all experts, all groups
     (128, 64, 8, 2, 1.0, None, 96, 600, 0.0),          # no groups; the tensor-core grouped product's sizes

@@ -80,9 +80,9 @@ CONFIGS = {
     # the tensor-core kernels' sizes: cache rows of 64 numbers with groups of four and eight query heads, a cache row of
     # 144 numbers (the wide latent kernel), retention heads of 64; all experts chosen; every group kept
     "C": config(128, 300, 1e-5, [
-        layer("attention", attention(2, 1, 32, 64, 0.18, 0.5, conv=3, rot={"base": 20000.0, "dims": 32}), moe(40, 4, 4, 1.5, (2, 2), 64)),
-        layer("latent_attention", latent(8, 32, 32, 64, 0.18, window=40), dense(160, 1.0)),
-        layer("retention", retention(2, 64, 64, [0.984375, 0.9990234375], rot={"base": 1000000.0, "dims": 32}), moe(40, 6, 2, 1.0, (2, 1), 24)),
+        layer("attention", attention(2, 1, 32, 64, 0.18, 0.4, conv=2, rot={"base": 20000.0, "dims": 16}), moe(40, 4, 4, 1.3, (2, 2), 64)),
+        layer("latent_attention", latent(8, 32, 48, 64, 0.2, window=37), dense(160, 1.2)),
+        layer("retention", retention(2, 64, 64, [0.97, 0.998], rot={"base": 500000.0, "dims": 32}), moe(40, 6, 2, 1.0, (2, 1), 24)),
         layer("latent_attention", latent(4, 16, 48, 144, 0.25), moe(40, 6, 2, 1.0, (3, 1))),
     ], 0.08),
     # sizes that no vector load divides: a width of 8 * 5, an odd vocabulary, maps of 6 with 2 rotated dims, one tap, a
