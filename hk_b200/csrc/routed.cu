@@ -580,7 +580,7 @@ __global__ void route_combine_kernel(const float* __restrict__ ys, const int* __
                                      const float* __restrict__ shared_gate) {
   const int t = blockIdx.x;
   const float sg = shared != nullptr ? (shared_gate != nullptr ? shared_gate[t] : 1.0f) : 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc = fmaf(weights[(size_t)t * top + k], ys[(size_t)inv[(size_t)t * top + k] * d + i], acc);
     if (shared != nullptr) acc = fmaf(sg, shared[(size_t)t * d + i], acc);
@@ -592,6 +592,10 @@ __global__ void route_combine_kernel(const float* __restrict__ ys, const int* __
 HK_API int hk_route_combine(const float* ys, const int* inv, const float* weights, float* y, int n, int d, int top, int accumulate,
                             const float* shared, const float* shared_gate, void* stream) {
   if (n <= 0) return 0;
-  return hk_launch(route_combine_kernel, dim3((unsigned)n), dim3(d >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, ys, inv, weights,
+  // a block per token; where the tokens alone do not fill the SMs (decode steps) a token's columns are spread over blocks
+  const int threads = d >= 1024 ? 256 : 128;
+  int split = 1;
+  while (split < 16 && (long long)n * split < 2 * 148 && split * threads < d) split <<= 1;
+  return hk_launch(route_combine_kernel, dim3((unsigned)n, (unsigned)split), dim3(threads), 0, (cudaStream_t)stream, ys, inv, weights,
                    y, d, top, accumulate, shared, shared_gate);
 }
