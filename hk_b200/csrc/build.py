@@ -43,7 +43,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_prefill_tc": "attention_prefill_tc.cu",
     "attention_latent": "attention_latent.cu",   # attention over a compressed cache whose rows are wider than a flash head
     "gemm_heads": "gemm_heads.cu",     # one small tensor-core product per head (a latent attention's up-projections)
-    "recurrent": "recurrent.cu",       # scans of the recurrent mixers (delta rule, minGRU)
+    "recurrent": "recurrent.cu",       # scans of the recurrent mixers (delta rules, minGRU, matrix memory, retention)
     "routed": "routed.cu",             # a feed-forward of experts: route, sort, grouped products, combine
     "runtime": "runtime.cpp",          # host only: the cache's books (no GPU code, no CUDA headers)
 }
